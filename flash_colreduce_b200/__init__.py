@@ -1,0 +1,12 @@
+"""flash_colreduce for NVIDIA B200 (sm_100a).
+
+Drop-in for the Python API of z-lab/flash-colreduce
+(flash_colreduce/__init__.py:1-4): ``flash_colreduce``, ``naive_colreduce``
+and ``__version__``.
+"""
+from .dense import naive_colreduce
+from .op import colreduce_partial, finalize_scores, flash_colreduce, valid_scores
+
+__version__ = "0.1.0"
+__all__ = ["flash_colreduce", "naive_colreduce", "colreduce_partial", "finalize_scores", "valid_scores",
+           "__version__"]

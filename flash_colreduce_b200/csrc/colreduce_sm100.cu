@@ -1,0 +1,918 @@
+// flash_colreduce for B200 (sm_100a): device kernels and the C ABI in front of them.
+//
+// The operator is computed in two streaming passes that share one kernel
+// template, each a warp-specialised persistent kernel:
+//
+//   rows pass  (PH_ROWS): a CTA keeps two 128-row Q tiles stationary in shared
+//       memory and streams K tiles past them.  S = Q.K^T lands in tensor
+//       memory with query rows on the 128 lanes, so each softmax thread owns
+//       one query row and keeps its running max / sum in registers.  Output:
+//       -log2-sum-exp2 of every row.
+//   columns pass (PH_COLS): the operands swap roles.  A CTA keeps two 128-row
+//       K tiles stationary and streams Q tiles, so S^T lands with key columns
+//       on the lanes; each softmax thread owns one key column and folds
+//       P = exp2(s*scale2 - lse_i) over the query dimension in a register.
+//       No atomics and no cross-thread reduction; splits of the query range
+//       go to a partial buffer that a last kernel combines in fixed order.
+//
+// Warp roles inside a CTA (320 threads): warps 0-3 and 4-7 are the two softmax
+// warpgroups (one per stationary tile), warp 8 issues TMA loads, warp 9 issues
+// tcgen05.mma and owns the tensor-memory allocation.
+//
+// The arithmetic follows the reference kernel: scores are scaled by
+// scale/ln(2) and exponentials are base 2 (flash_colreduce/flash.py:59-78,
+// :108-124, :242, :291); masks follow flash.py:11-32; the causal tile ranges
+// follow flash.py:201-207 but at 128-row granularity and with fully masked
+// tiles never scheduled.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <mutex>
+#include <string>
+
+#include "plan.h"
+#include "ptx_sm100.cuh"
+
+namespace fcr {
+
+enum { PH_DUMP = 0, PH_ROWS = 1, PH_COLS = 2 };
+enum { RED_SUM = 0, RED_MAX = 1 };
+
+constexpr int kSoftmaxWarps = 8;
+constexpr int kProducerWarp = 8;
+constexpr int kMmaWarp = 9;
+constexpr int kThreads = 320;
+constexpr int kTmemCols = 512;
+constexpr long long kWaitLimitCycles = 2000000000LL;  // about one second
+
+// Device status codes (status word 0).  Word 1: block, word 2: thread, word 3: detail.
+enum {
+  ST_OK = 0,
+  ST_SMEM_MISALIGNED = 1,
+  ST_WAIT_STAT_EMPTY = 11,
+  ST_WAIT_RING_EMPTY = 12,
+  ST_WAIT_STAT_FULL = 21,
+  ST_WAIT_RING_FULL = 22,
+  ST_WAIT_TMEM_EMPTY = 23,
+  ST_WAIT_DRAIN = 24,
+  ST_WAIT_TMEM_FULL = 31,
+  ST_WAIT_RING_FULL_SM = 32,
+};
+
+struct PassParams : PassGeom {
+  int m_pad, n_pad;
+  float scale2;    // |scale| * log2(e)
+  uint32_t idesc;  // tcgen05 instruction descriptor
+  float* neg_lse;  // [BH][m_pad]
+  float* part_m;   // [n_split][BH][m_pad]
+  float* part_l;   // [n_split][BH][m_pad]
+  float* part_out; // [n_split][BH][n_pad]
+  float* dump;     // [BH][m_pad][n_pad]   (PH_DUMP)
+  void* out;       // [BH][N] of out_dtype
+  int out_dtype;
+  int mean_mode;   // 0: none, 1: divide by div_M, 2: causal rule
+  int div_M, div_N, div_c;
+  int* status;
+};
+
+template <int DPAD>
+struct SmemLayout {
+  static constexpr int kTileBytes = kTile * DPAD * 2;
+  static constexpr int kHalves = DPAD / 64;     // 64-element (128-byte) column slabs per tile
+  static constexpr int kHalfBytes = kTile * 128;
+  static constexpr int KS = 2;                  // stationary stages (items in flight)
+  static constexpr int KR = (DPAD == 128) ? 3 : 6;  // streamed ring stages
+  static constexpr int kLseBytes = kTile * 4;
+  static constexpr int off_stat = 0;
+  static constexpr int off_ring = off_stat + KS * kSubTiles * kTileBytes;
+  static constexpr int off_lse = off_ring + KR * kTileBytes;
+  static constexpr int off_bars = off_lse + KR * kLseBytes;
+  static constexpr int kNumBars = 2 * KS + 2 * KR + 8;
+  static constexpr int off_misc = off_bars + 8 * kNumBars;
+  static constexpr int kBytes = off_misc + 16;
+  static constexpr int kDynamicBytes = kBytes + 1024;  // slack for manual 1024-byte alignment
+  static_assert(kDynamicBytes <= 232448, "exceeds the 227 KB shared memory of an sm_100 CTA");
+};
+
+__device__ __noinline__ void report_status(int* status, int code, int detail) {
+  if (atomicCAS(status, 0, code) == 0) {
+    status[1] = (int)blockIdx.x;
+    status[2] = (int)threadIdx.x;
+    status[3] = detail;
+    __threadfence();
+  }
+}
+
+// Bounded mbarrier wait.  Returns false when the wait limit expired here or in
+// another thread of the CTA (the abort flag); the caller then leaves its loop.
+__device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                         int* status, int code) {
+  if (ptx::mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  uint32_t spins = 0;
+  while (true) {
+    if (ptx::mbar_try_wait(bar, parity)) return true;
+    if ((++spins & 63u) == 0) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > kWaitLimitCycles) {
+        *abort_flag = 1;
+        report_status(status, code, (int)parity);
+        return false;
+      }
+    }
+  }
+}
+// Same, with a warp-uniform result so that .sync.aligned instructions that
+// follow are executed by all 32 lanes or by none.
+__device__ __forceinline__ bool wait_bar_warp(uint32_t bar, uint32_t parity,
+                                              volatile int* abort_flag, int* status, int code) {
+  const bool ok = wait_bar(bar, parity, abort_flag, status, code);
+  return __all_sync(0xffffffffu, ok);
+}
+
+__device__ __forceinline__ float mean_divisor(const PassParams& p, int j) {
+  if (p.mean_mode == 2 && j >= p.div_c) return (float)(p.div_N - j);
+  return (float)p.div_M;
+}
+
+__device__ __forceinline__ void store_out(void* out, int out_dtype, size_t idx, float v) {
+  if (out_dtype == FCR_F16) {
+    reinterpret_cast<__half*>(out)[idx] = __float2half_rn(v);
+  } else if (out_dtype == FCR_BF16) {
+    reinterpret_cast<__nv_bfloat16*>(out)[idx] = __float2bfloat16_rn(v);
+  } else {
+    reinterpret_cast<float*>(out)[idx] = v;
+  }
+}
+
+// ---------------------------------------------------------------- rows pass
+// One 32-column chunk of a query row: online max / sum in the base-2 domain
+// (flash_colreduce/flash.py:71-78).  `nvalid` = number of leading columns of
+// the chunk this row may attend (only read when MASKED).
+template <bool MASKED>
+__device__ __forceinline__ void rows_chunk(const uint32_t (&r)[32], float scale2, int nvalid,
+                                           float& m_run, float& l_run) {
+  float x[32];
+#pragma unroll
+  for (int e = 0; e < 32; ++e) {
+    x[e] = __uint_as_float(r[e]);
+    if (MASKED && e >= nvalid) x[e] = -INFINITY;
+  }
+  float mx0 = fmaxf(x[0], x[1]), mx1 = fmaxf(x[2], x[3]);
+#pragma unroll
+  for (int e = 4; e < 32; e += 4) {
+    mx0 = fmaxf(mx0, fmaxf(x[e], x[e + 1]));
+    mx1 = fmaxf(mx1, fmaxf(x[e + 2], x[e + 3]));
+  }
+  const float m_new = fmaxf(m_run, fmaxf(mx0, mx1) * scale2);
+  const float m_safe = (m_new == -INFINITY) ? 0.f : m_new;  // row sees nothing yet
+  const float alpha = ptx::ex2(m_run - m_safe);
+  const float nm = -m_safe;
+  float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+#pragma unroll
+  for (int e = 0; e < 32; e += 4) {
+    s0 += ptx::ex2(fmaf(x[e], scale2, nm));
+    s1 += ptx::ex2(fmaf(x[e + 1], scale2, nm));
+    s2 += ptx::ex2(fmaf(x[e + 2], scale2, nm));
+    s3 += ptx::ex2(fmaf(x[e + 3], scale2, nm));
+  }
+  l_run = fmaf(l_run, alpha, (s0 + s1) + (s2 + s3));
+  m_run = m_new;
+}
+
+// ------------------------------------------------------------- columns pass
+// One 32-query chunk of a key column: P = exp2(s*scale2 - lse_i) folded into
+// the column's accumulators (flash_colreduce/flash.py:120-124).  Queries
+// e in [e_lo, e_hi) of the chunk are valid (only read when MASKED).  For max
+// the fold is done on the exponent, exp2 being monotonic.
+template <int RED, bool MASKED>
+__device__ __forceinline__ void cols_chunk(const uint32_t (&r)[32], const float* neg_lse,
+                                           float scale2, int e_lo, int e_hi, float (&acc)[4]) {
+#pragma unroll
+  for (int q = 0; q < 8; ++q) {
+    const float4 nl = reinterpret_cast<const float4*>(neg_lse)[q];
+    const float nlv[4] = {nl.x, nl.y, nl.z, nl.w};
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int e = q * 4 + u;
+      float t = fmaf(__uint_as_float(r[e]), scale2, nlv[u]);
+      const bool valid = !MASKED || (e >= e_lo && e < e_hi);
+      if (RED == RED_SUM) {
+        float pr = ptx::ex2(t);
+        if (MASKED) pr = valid ? pr : 0.f;
+        acc[u] += pr;
+      } else {
+        if (MASKED) t = valid ? t : -INFINITY;
+        acc[u] = fmaxf(acc[u], t);
+      }
+    }
+  }
+}
+
+template <int PHASE, int DPAD, int RED>
+__global__ void __launch_bounds__(kThreads, 1)
+pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
+            const __grid_constant__ CUtensorMap tmap_strm, const PassParams p) {
+  using L = SmemLayout<DPAD>;
+  constexpr int KS = L::KS, KR = L::KR;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = ptx::smem_u32(smem_raw);
+  const uint32_t base = (raw_addr + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (base - raw_addr);
+
+  const uint32_t s_stat = base + L::off_stat;
+  const uint32_t s_ring = base + L::off_ring;
+  const uint32_t s_lse = base + L::off_lse;
+  const uint32_t bar0 = base + L::off_bars;
+  auto bar_stat_full = [&](uint32_t ks) { return bar0 + 8u * ks; };
+  auto bar_stat_empty = [&](uint32_t ks) { return bar0 + 8u * (KS + ks); };
+  auto bar_ring_full = [&](uint32_t s) { return bar0 + 8u * (2 * KS + s); };
+  auto bar_ring_empty = [&](uint32_t s) { return bar0 + 8u * (2 * KS + KR + s); };
+  auto bar_tm_full = [&](uint32_t a, uint32_t ts) { return bar0 + 8u * (2 * KS + 2 * KR + a * 2 + ts); };
+  auto bar_tm_empty = [&](uint32_t a, uint32_t ts) {
+    return bar0 + 8u * (2 * KS + 2 * KR + 4 + a * 2 + ts);
+  };
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + L::off_misc);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::off_misc + 4);
+
+  const int warp = (int)(threadIdx.x >> 5);
+  const int lane = (int)(threadIdx.x & 31);
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < KS; ++i) {
+      ptx::mbar_init(bar_stat_full(i), 1);
+      ptx::mbar_init(bar_stat_empty(i), 1);
+    }
+    for (int i = 0; i < KR; ++i) {
+      ptx::mbar_init(bar_ring_full(i), 1);
+      ptx::mbar_init(bar_ring_empty(i), PHASE == PH_COLS ? 1 + kSoftmaxWarps : 1);
+    }
+    for (int a = 0; a < 2; ++a)
+      for (int ts = 0; ts < 2; ++ts) {
+        ptx::mbar_init(bar_tm_full(a, ts), 1);
+        ptx::mbar_init(bar_tm_empty(a, ts), 4);
+      }
+    *abort_flag = 0;
+    ptx::fence_mbar_init();
+  }
+  if (warp == kMmaWarp) {
+    ptx::tmem_alloc(ptx::smem_u32(const_cast<uint32_t*>(tmem_slot)), kTmemCols);
+    ptx::tmem_relinquish();
+  }
+  if (warp == kProducerWarp && lane == 0) {
+    ptx::prefetch_tensormap(&tmap_stat);
+    ptx::prefetch_tensormap(&tmap_strm);
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  ptx::tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == kProducerWarp) {
+    // ------------------------------------------------------------ TMA warp
+    uint32_t ring_seq = 0, item_seq = 0;
+    bool ok = true;
+    for (int item = (int)blockIdx.x; ok && item < p.n_items; item += (int)gridDim.x, ++item_seq) {
+      const Item g = decode_item<PHASE == PH_COLS>(p, item);
+      const int b = g.bh / p.H, h = g.bh - b * p.H;
+      const uint32_t ks = item_seq % KS, kph = (item_seq / KS) & 1u;
+      ok = wait_bar_warp(bar_stat_empty(ks), kph ^ 1u, abort_flag, p.status, ST_WAIT_STAT_EMPTY);
+      if (!ok) break;
+      if (lane == 0) {
+        ptx::mbar_arrive_expect_tx(bar_stat_full(ks), kSubTiles * L::kTileBytes);
+#pragma unroll
+        for (int a = 0; a < kSubTiles; ++a)
+#pragma unroll
+          for (int hf = 0; hf < L::kHalves; ++hf)
+            ptx::tma_load_4d(s_stat + (ks * kSubTiles + a) * L::kTileBytes + hf * L::kHalfBytes,
+                             &tmap_stat, bar_stat_full(ks), hf * 64, g.r0[a], h, b);
+      }
+      __syncwarp();
+      for (int t = g.c_lo; t < g.c_hi; ++t, ++ring_seq) {
+        const uint32_t s = ring_seq % KR, ph = (ring_seq / KR) & 1u;
+        ok = wait_bar_warp(bar_ring_empty(s), ph ^ 1u, abort_flag, p.status, ST_WAIT_RING_EMPTY);
+        if (!ok) break;
+        if (lane == 0) {
+          ptx::mbar_arrive_expect_tx(bar_ring_full(s),
+                                     L::kTileBytes + (PHASE == PH_COLS ? L::kLseBytes : 0));
+#pragma unroll
+          for (int hf = 0; hf < L::kHalves; ++hf)
+            ptx::tma_load_4d(s_ring + s * L::kTileBytes + hf * L::kHalfBytes, &tmap_strm,
+                             bar_ring_full(s), hf * 64, t * kTile, h, b);
+          if (PHASE == PH_COLS)
+            ptx::bulk_load(s_lse + s * L::kLseBytes,
+                           p.neg_lse + (size_t)g.bh * p.m_pad + (size_t)t * kTile, L::kLseBytes,
+                           bar_ring_full(s));
+        }
+        __syncwarp();
+      }
+    }
+  } else if (warp == kMmaWarp) {
+    // ------------------------------------------------------------ MMA warp
+    uint32_t ring_seq = 0, item_seq = 0;
+    uint32_t tm_seq[kSubTiles] = {0, 0};
+    bool ok = true;
+    for (int item = (int)blockIdx.x; ok && item < p.n_items; item += (int)gridDim.x, ++item_seq) {
+      const Item g = decode_item<PHASE == PH_COLS>(p, item);
+      const uint32_t ks = item_seq % KS, kph = (item_seq / KS) & 1u;
+      ok = wait_bar_warp(bar_stat_full(ks), kph, abort_flag, p.status, ST_WAIT_STAT_FULL);
+      if (!ok) break;
+      ptx::tc_fence_after_sync();
+      for (int t = g.c_lo; ok && t < g.c_hi; ++t, ++ring_seq) {
+        const uint32_t s = ring_seq % KR, ph = (ring_seq / KR) & 1u;
+        ok = wait_bar_warp(bar_ring_full(s), ph, abort_flag, p.status, ST_WAIT_RING_FULL);
+        if (!ok) break;
+        ptx::tc_fence_after_sync();
+#pragma unroll
+        for (int a = 0; a < kSubTiles; ++a) {
+          if (ok && t >= g.t_lo[a] && t < g.t_hi[a]) {
+            const uint32_t ts = tm_seq[a] & 1u, tph = (tm_seq[a] >> 1) & 1u;
+            ok = wait_bar_warp(bar_tm_empty(a, ts), tph ^ 1u, abort_flag, p.status,
+                               ST_WAIT_TMEM_EMPTY);
+            if (ok) {
+              ptx::tc_fence_after_sync();
+              if (lane == 0) {
+                const uint32_t d = tmem_base + (uint32_t)(a * 2 + ts) * kTile;
+                const uint32_t a_addr = s_stat + (ks * kSubTiles + a) * L::kTileBytes;
+                const uint32_t b_addr = s_ring + s * L::kTileBytes;
+#pragma unroll
+                for (int kk = 0; kk < DPAD / 16; ++kk) {
+                  const uint32_t koff = (uint32_t)(kk >> 2) * L::kHalfBytes + (uint32_t)(kk & 3) * 32u;
+                  ptx::umma_f16(d, ptx::smem_desc_sw128(a_addr + koff),
+                                ptx::smem_desc_sw128(b_addr + koff), p.idesc, kk > 0 ? 1u : 0u);
+                }
+                ptx::umma_commit(bar_tm_full(a, ts));
+              }
+              __syncwarp();
+              ++tm_seq[a];
+            }
+          }
+        }
+        if (ok && lane == 0) ptx::umma_commit(bar_ring_empty(s));
+        __syncwarp();
+      }
+      if (ok && lane == 0) ptx::umma_commit(bar_stat_empty(ks));
+      __syncwarp();
+    }
+    if (ok && item_seq > 0) {
+      // The last commit covers every MMA issued: wait for it so that no
+      // asynchronous arrive is still outstanding when the CTA retires.
+      const uint32_t last = item_seq - 1;
+      wait_bar_warp(bar_stat_empty(last % KS), (last / KS) & 1u, abort_flag, p.status,
+                    ST_WAIT_DRAIN);
+    }
+  } else {
+    // -------------------------------------------------------- softmax warps
+    const int a = warp >> 2;
+    const int tid_wg = (warp & 3) * 32 + lane;
+    const uint32_t lane_field = (uint32_t)((warp & 3) * 32) << 16;
+    uint32_t ring_base = 0, tm_seq = 0;
+    bool ok = true;
+    for (int item = (int)blockIdx.x; ok && item < p.n_items; item += (int)gridDim.x) {
+      const Item g = decode_item<PHASE == PH_COLS>(p, item);
+      const int mine = g.r0[a] + tid_wg;  // query row (rows pass) or key column (columns pass)
+      float m_run = -INFINITY, l_run = 0.f;
+      float acc[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) acc[u] = (RED == RED_MAX) ? -INFINITY : 0.f;
+
+      for (int t = g.c_lo; ok && t < g.c_hi; ++t) {
+        const bool active = (t >= g.t_lo[a]) && (t < g.t_hi[a]);
+        const uint32_t rs = ring_base + (uint32_t)(t - g.c_lo);
+        const uint32_t s = rs % KR, rph = (rs / KR) & 1u;
+        if (PHASE == PH_COLS) {
+          ok = wait_bar_warp(bar_ring_full(s), rph, abort_flag, p.status, ST_WAIT_RING_FULL_SM);
+          if (!ok) break;
+        }
+        if (active) {
+          const uint32_t ts = tm_seq & 1u, tph = (tm_seq >> 1) & 1u;
+          ok = wait_bar_warp(bar_tm_full(a, ts), tph, abort_flag, p.status, ST_WAIT_TMEM_FULL);
+          if (!ok) break;
+          ptx::tc_fence_after_sync();
+          const uint32_t taddr = tmem_base + lane_field + (uint32_t)(a * 2 + ts) * kTile;
+          const int c0 = t * kTile;  // first streamed index of the tile
+          bool need_mask;
+          int lim_lo = 0, lim_hi = 0;
+          if (PHASE == PH_COLS) {
+            // valid queries i: max(mine - off, 0) <= i < M
+            need_mask = (c0 + kTile > p.M) || (p.causal && (c0 + p.off < g.r0[a] + kTile - 1));
+            lim_lo = p.causal ? max(mine - p.off, 0) - c0 : -(1 << 30);
+            lim_hi = p.M - c0;
+          } else {
+            // valid keys j: j <= min(N - 1, mine + off)
+            need_mask = (c0 + kTile > p.N) || (p.causal && (c0 + kTile - 1 > g.r0[a] + p.off));
+            const long long jlim =
+                p.causal ? min((long long)p.N - 1, (long long)mine + p.off) : (long long)p.N - 1;
+            lim_hi = (int)(jlim - c0 + 1);
+          }
+          if (PHASE == PH_DUMP) need_mask = false;
+          const float* lse_s = reinterpret_cast<const float*>(smem + L::off_lse + s * L::kLseBytes);
+
+          uint32_t ra[32], rb[32];
+          auto consume = [&](const uint32_t (&r)[32], int c) {
+            if constexpr (PHASE == PH_DUMP) {
+              if (mine < p.m_pad) {
+                float4* dst = reinterpret_cast<float4*>(
+                    p.dump + ((size_t)g.bh * p.m_pad + mine) * p.n_pad + c0 + 32 * c);
+#pragma unroll
+                for (int q = 0; q < 8; ++q)
+                  dst[q] = make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
+                                       __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
+              }
+            } else if constexpr (PHASE == PH_ROWS) {
+              if (need_mask)
+                rows_chunk<true>(r, p.scale2, lim_hi - 32 * c, m_run, l_run);
+              else
+                rows_chunk<false>(r, p.scale2, 32, m_run, l_run);
+            } else {
+              if (need_mask)
+                cols_chunk<RED, true>(r, lse_s + 32 * c, p.scale2, lim_lo - 32 * c,
+                                      lim_hi - 32 * c, acc);
+              else
+                cols_chunk<RED, false>(r, lse_s + 32 * c, p.scale2, 0, 32, acc);
+            }
+          };
+          ptx::tmem_ld32(taddr, ra);
+          ptx::tmem_ld_wait(ra);
+          ptx::tmem_ld32(taddr + 32, rb);
+          consume(ra, 0);
+          ptx::tmem_ld_wait(rb);
+          ptx::tmem_ld32(taddr + 64, ra);
+          consume(rb, 1);
+          ptx::tmem_ld_wait(ra);
+          ptx::tmem_ld32(taddr + 96, rb);
+          consume(ra, 2);
+          ptx::tmem_ld_wait(rb);
+          // every lane has its copy of the tile: hand the accumulator back
+          ptx::tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive(bar_tm_empty(a, ts));
+          consume(rb, 3);
+          ++tm_seq;
+        }
+        if (PHASE == PH_COLS) {
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive(bar_ring_empty(s));
+        }
+      }
+      ring_base += (uint32_t)(g.c_hi - g.c_lo);
+      if (!ok) break;
+
+      // ------------------------------------------------------ item epilogue
+      if (PHASE == PH_ROWS) {
+        if (mine < p.M && g.r0[a] < p.LS) {
+          if (p.n_split == 1) {
+            p.neg_lse[(size_t)g.bh * p.m_pad + mine] = -(m_run + log2f(l_run));
+          } else {
+            const size_t idx = ((size_t)g.sp * p.BH + g.bh) * p.m_pad + mine;
+            p.part_m[idx] = m_run;
+            p.part_l[idx] = l_run;
+          }
+        }
+      } else if (PHASE == PH_COLS) {
+        if (mine < p.N) {
+          float v;
+          if (RED == RED_SUM)
+            v = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+          else
+            v = ptx::ex2(fmaxf(fmaxf(acc[0], acc[1]), fmaxf(acc[2], acc[3])));
+          if (p.n_split == 1) {
+            if (p.mean_mode) v = v / mean_divisor(p, mine);
+            store_out(p.out, p.out_dtype, (size_t)g.bh * p.N + mine, v);
+          } else {
+            p.part_out[((size_t)g.sp * p.BH + g.bh) * p.n_pad + mine] = v;
+          }
+        }
+      }
+    }
+  }
+
+  // ------------------------------------------------------------- teardown
+  __syncwarp();
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag) {
+    // A wait expired somewhere: give loads that may still be in flight time to
+    // land in this CTA's shared memory before it is released.
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == kMmaWarp) {
+    ptx::tc_fence_after_sync();
+    ptx::tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// Combines the per-split running (max, sum) of the rows pass into -lse.
+__global__ void combine_lse_kernel(const float* __restrict__ part_m,
+                                   const float* __restrict__ part_l, float* __restrict__ neg_lse,
+                                   int n_split, size_t per_split, int m_pad, int M) {
+  const size_t total = per_split;
+  for (size_t idx = blockIdx.x * (size_t)blockDim.x + threadIdx.x; idx < total;
+       idx += (size_t)gridDim.x * blockDim.x) {
+    const int i = (int)(idx % m_pad);
+    if (i >= M) continue;
+    float mx = -INFINITY;
+    for (int s = 0; s < n_split; ++s) mx = fmaxf(mx, part_m[s * per_split + idx]);
+    float l = 0.f;
+    for (int s = 0; s < n_split; ++s) {
+      const float ms = part_m[s * per_split + idx];
+      if (ms != -INFINITY) l = fmaf(part_l[s * per_split + idx], exp2f(ms - mx), l);
+    }
+    neg_lse[idx] = -(mx + log2f(l));
+  }
+}
+
+// Combines the per-split column partials in split order, applies the mean
+// divisor and casts (flash_colreduce/flash.py:308, :377-385).
+__global__ void final_reduce_kernel(const float* __restrict__ part, PassParams p, int is_max) {
+  const size_t per_split = (size_t)p.BH * p.n_pad;
+  for (size_t idx = blockIdx.x * (size_t)blockDim.x + threadIdx.x; idx < per_split;
+       idx += (size_t)gridDim.x * blockDim.x) {
+    const int j = (int)(idx % p.n_pad);
+    if (j >= p.N) continue;
+    const size_t bh = idx / p.n_pad;
+    float v = part[idx];
+    for (int s = 1; s < p.n_split; ++s) {
+      const float w = part[s * per_split + idx];
+      v = is_max ? fmaxf(v, w) : v + w;
+    }
+    if (p.mean_mode) v = v / mean_divisor(p, j);
+    store_out(p.out, p.out_dtype, bh * p.N + j, v);
+  }
+}
+
+// Mean divisor + cast of an already reduced fp32 (B*H, N) array.
+__global__ void finalize_kernel(const float* __restrict__ acc, PassParams p) {
+  const size_t total = (size_t)p.BH * p.N;
+  for (size_t idx = blockIdx.x * (size_t)blockDim.x + threadIdx.x; idx < total;
+       idx += (size_t)gridDim.x * blockDim.x) {
+    const int j = (int)(idx % p.N);
+    float v = acc[idx];
+    if (p.mean_mode) v = v / mean_divisor(p, j);
+    store_out(p.out, p.out_dtype, idx, v);
+  }
+}
+
+__global__ void ex2_probe_kernel(float* sink, int iters) {
+  float v[8];
+#pragma unroll
+  for (int u = 0; u < 8; ++u) v[u] = -1.0f - 0.001f * (float)(threadIdx.x + u);
+  for (int it = 0; it < iters; ++it) {
+#pragma unroll
+    for (int u = 0; u < 8; ++u) v[u] = ptx::ex2(v[u]) - 1.5f;
+  }
+  float s = 0.f;
+#pragma unroll
+  for (int u = 0; u < 8; ++u) s += v[u];
+  if (s == 123.456f) sink[0] = s;
+}
+
+// ===================================================================== host
+static thread_local std::string g_last_error;
+
+static int fail(int code, const std::string& msg) {
+  g_last_error = msg;
+  return code;
+}
+static int cuda_fail(cudaError_t e, const char* what) {
+  return fail(FCR_ERR_CUDA, std::string(what) + ": " + cudaGetErrorString(e));
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = []() -> EncodeTiledFn {
+    void* f = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) !=
+            cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      return nullptr;
+    return reinterpret_cast<EncodeTiledFn>(f);
+  }();
+  return fn;
+}
+
+// Tensor map over a (B,H,rows,D) tensor viewed as 4-D (D, rows, H, B); a box
+// is 64 elements x 128 rows of one head, written to shared memory with the
+// 128-byte swizzle.  Elements beyond D or beyond `rows` read as zero.
+static int make_tensor_map(CUtensorMap* map, const void* ptr, int dtype, int D, int rows, int H,
+                           int B, const int64_t* strides) {
+  EncodeTiledFn enc = encode_tiled_fn();
+  if (!enc) return fail(FCR_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  if ((reinterpret_cast<uintptr_t>(ptr) & 15u) != 0)
+    return fail(FCR_ERR_UNSUPPORTED, "q / k base address must be 16-byte aligned");
+  const int64_t fallback = align_up64((int64_t)D, 8);
+  auto stride_bytes = [&](int dim, int64_t s) -> cuuint64_t {
+    if (dim <= 1 && (s <= 0 || s % 8 != 0)) s = fallback;  // never dereferenced
+    return (cuuint64_t)s * 2u;
+  };
+  cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)rows, (cuuint64_t)H, (cuuint64_t)B};
+  cuuint64_t gstr[3] = {stride_bytes(rows, strides[2]), stride_bytes(H, strides[1]),
+                        stride_bytes(B, strides[0])};
+  cuuint32_t box[4] = {64u, (cuuint32_t)kTile, 1u, 1u};
+  cuuint32_t estr[4] = {1u, 1u, 1u, 1u};
+  const CUtensorMapDataType dt =
+      dtype == FCR_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  const CUresult r = enc(map, dt, 4, const_cast<void*>(ptr), dims, gstr, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return fail(FCR_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult " + std::to_string((int)r));
+  return FCR_OK;
+}
+
+static int device_sm_count(int* out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+  int major = 0, sms = 0;
+  e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaDeviceGetAttribute");
+  if (major != 10)
+    return fail(FCR_ERR_UNSUPPORTED,
+                "this library contains sm_100a code only; the current device has compute capability major " +
+                    std::to_string(major));
+  e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaDeviceGetAttribute");
+  *out = sms;
+  return FCR_OK;
+}
+
+static uint32_t instr_desc(int dtype, bool negate_a) {
+  // kind::f16, fp32 accumulate, both operands K-major, M = 128, N = 128
+  const uint32_t fmt = dtype == FCR_BF16 ? 1u : 0u;
+  return (1u << 4) | (fmt << 7) | (fmt << 10) | ((negate_a ? 1u : 0u) << 13) |
+         ((uint32_t)(kTile >> 3) << 17) | ((uint32_t)(kTile >> 4) << 24);
+}
+
+template <int PHASE, int DPAD, int RED>
+static int launch_pass(const CUtensorMap& stat, const CUtensorMap& strm, const PassParams& pp,
+                       int ctas, cudaStream_t stream) {
+  auto kern = pass_kernel<PHASE, DPAD, RED>;
+  constexpr int smem = SmemLayout<DPAD>::kDynamicBytes;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute");
+  kern<<<ctas, kThreads, smem, stream>>>(stat, strm, pp);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "pass kernel launch");
+  return FCR_OK;
+}
+
+template <int PHASE, int RED>
+static int launch_pass_d(int d_pad, const CUtensorMap& stat, const CUtensorMap& strm,
+                         const PassParams& pp, int ctas, cudaStream_t stream) {
+  if (d_pad == 64) return launch_pass<PHASE, 64, RED>(stat, strm, pp, ctas, stream);
+  return launch_pass<PHASE, 128, RED>(stat, strm, pp, ctas, stream);
+}
+
+static int check_workspace(const fcr_plan& pl, const void* ws, size_t ws_bytes) {
+  if (!ws) return fail(FCR_ERR_WORKSPACE, "workspace is null");
+  if ((reinterpret_cast<uintptr_t>(ws) & 255u) != 0)
+    return fail(FCR_ERR_WORKSPACE, "workspace must be 256-byte aligned");
+  if ((int64_t)ws_bytes < pl.workspace_bytes)
+    return fail(FCR_ERR_WORKSPACE, "workspace of " + std::to_string(ws_bytes) +
+                                       " bytes is smaller than the required " +
+                                       std::to_string(pl.workspace_bytes));
+  return FCR_OK;
+}
+
+static void fill_common(PassParams& pp, const fcr_problem& pr, const fcr_plan& pl, uint8_t* ws,
+                        bool cols) {
+  memset(&pp, 0, sizeof(pp));
+  static_cast<PassGeom&>(pp) = pass_geometry(pr, pl, cols);
+  pp.m_pad = pl.m_pad;
+  pp.n_pad = pl.n_pad;
+  float s2 = fabsf(pr.scale) * 1.4426950408889634f;
+  if (!(s2 >= 1e-30f)) s2 = 1e-30f;  // scale 0: every score becomes (numerically) zero
+  pp.scale2 = s2;
+  pp.idesc = instr_desc(pr.in_dtype, pr.scale < 0.f);
+  pp.neg_lse = reinterpret_cast<float*>(ws + pl.off_neg_lse);
+  pp.part_m = reinterpret_cast<float*>(ws + pl.off_part_m);
+  pp.part_l = reinterpret_cast<float*>(ws + pl.off_part_l);
+  pp.part_out = reinterpret_cast<float*>(ws + pl.off_part_out);
+  pp.status = reinterpret_cast<int*>(ws + pl.off_status);
+}
+
+static void fill_mean(PassParams& pp, int reduction, int is_causal, int M, int N) {
+  pp.div_M = M;
+  pp.div_N = N;
+  pp.div_c = N > M ? N - M : 0;
+  pp.mean_mode = reduction == FCR_MEAN ? (is_causal ? 2 : 1) : 0;
+}
+
+}  // namespace fcr
+
+using namespace fcr;
+
+extern "C" {
+
+const char* fcr_version(void) { return "0.1.0"; }
+
+const char* fcr_last_error(void) { return g_last_error.c_str(); }
+
+int fcr_plan_problem(const fcr_problem* problem, int32_t num_sms, fcr_plan* plan) {
+  if (!problem || !plan) return fail(FCR_ERR_BAD_ARG, "null problem or plan");
+  int sms = num_sms;
+  if (sms <= 0) {
+    const int rc = device_sm_count(&sms);
+    if (rc != FCR_OK) return rc;
+  }
+  std::string err;
+  const int rc = plan_problem(*problem, sms, *plan, err);
+  if (rc != FCR_OK) return fail(rc, err);
+  return FCR_OK;
+}
+
+int fcr_plan_item(const fcr_problem* problem, const fcr_plan* plan, int32_t pass, int32_t item,
+                  int32_t* out) {
+  if (!problem || !plan || !out) return fail(FCR_ERR_BAD_ARG, "null argument");
+  if (pass != 1 && pass != 2) return fail(FCR_ERR_BAD_ARG, "pass must be 1 (rows) or 2 (columns)");
+  const PassGeom g = pass_geometry(*problem, *plan, pass == 2);
+  if (item < 0 || item >= g.n_items) return fail(FCR_ERR_BAD_ARG, "item out of range");
+  const Item it = pass == 2 ? decode_item<true>(g, item) : decode_item<false>(g, item);
+  out[0] = it.bh;
+  out[1] = it.sp;
+  out[2] = it.c_lo;
+  out[3] = it.c_hi;
+  for (int a = 0; a < kSubTiles; ++a) {
+    out[4 + 3 * a] = it.r0[a];
+    out[5 + 3 * a] = it.t_lo[a];
+    out[6 + 3 * a] = it.t_hi[a];
+  }
+  return FCR_OK;
+}
+
+size_t fcr_workspace_bytes(const fcr_problem* problem, int32_t num_sms) {
+  fcr_plan pl;
+  if (fcr_plan_problem(problem, num_sms, &pl) != FCR_OK) return 0;
+  return (size_t)pl.workspace_bytes;
+}
+
+int fcr_colreduce(const fcr_problem* problem, const void* q, const void* k, void* out,
+                  int32_t out_dtype, void* workspace, size_t workspace_bytes, void* stream_v) {
+  if (!problem || !q || !k || !out) return fail(FCR_ERR_BAD_ARG, "null argument");
+  if (out_dtype != FCR_F16 && out_dtype != FCR_BF16 && out_dtype != FCR_F32)
+    return fail(FCR_ERR_BAD_ARG, "invalid out_dtype");
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
+  fcr_plan pl;
+  int rc = fcr_plan_problem(problem, 0, &pl);
+  if (rc != FCR_OK) return rc;
+  rc = check_workspace(pl, workspace, workspace_bytes);
+  if (rc != FCR_OK) return rc;
+  const fcr_problem& pr = *problem;
+  uint8_t* ws = reinterpret_cast<uint8_t*>(workspace);
+
+  CUtensorMap map_q, map_k;
+  rc = make_tensor_map(&map_q, q, pr.in_dtype, pr.D, pr.M, pr.H, pr.B, pr.q_strides);
+  if (rc != FCR_OK) return rc;
+  rc = make_tensor_map(&map_k, k, pr.in_dtype, pr.D, pr.N, pr.H, pr.B, pr.k_strides);
+  if (rc != FCR_OK) return rc;
+
+  cudaError_t e = cudaMemsetAsync(ws + pl.off_status, 0, kStatusWords * 4, stream);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaMemsetAsync");
+
+  // rows pass: Q stationary, K streamed
+  PassParams pp;
+  fill_common(pp, pr, pl, ws, false);
+  rc = launch_pass_d<PH_ROWS, RED_SUM>(pl.d_pad, map_q, map_k, pp, pl.row_ctas, stream);
+  if (rc != FCR_OK) return rc;
+  if (pl.row_splits > 1) {
+    const size_t per_split = (size_t)pp.BH * pl.m_pad;
+    const int blocks = (int)std::min<size_t>((per_split + 255) / 256, 4096);
+    combine_lse_kernel<<<blocks, 256, 0, stream>>>(pp.part_m, pp.part_l, pp.neg_lse, pl.row_splits,
+                                                   per_split, pl.m_pad, pr.M);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e, "combine_lse launch");
+  }
+
+  // columns pass: K stationary, Q streamed
+  fill_common(pp, pr, pl, ws, true);
+  pp.out = out;
+  pp.out_dtype = out_dtype;
+  fill_mean(pp, pr.reduction, pr.is_causal, pr.mean_M > 0 ? pr.mean_M : pr.M,
+            pr.mean_N > 0 ? pr.mean_N : pr.N);
+  if (pr.reduction == FCR_MAX)
+    rc = launch_pass_d<PH_COLS, RED_MAX>(pl.d_pad, map_k, map_q, pp, pl.col_ctas, stream);
+  else
+    rc = launch_pass_d<PH_COLS, RED_SUM>(pl.d_pad, map_k, map_q, pp, pl.col_ctas, stream);
+  if (rc != FCR_OK) return rc;
+  if (pl.col_splits > 1) {
+    const size_t per_split = (size_t)pp.BH * pl.n_pad;
+    const int blocks = (int)std::min<size_t>((per_split + 255) / 256, 4096);
+    final_reduce_kernel<<<blocks, 256, 0, stream>>>(pp.part_out, pp, pr.reduction == FCR_MAX);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e, "final_reduce launch");
+  }
+  return FCR_OK;
+}
+
+int fcr_finalize(const float* acc, void* out, int32_t out_dtype, int32_t B, int32_t H, int32_t M,
+                 int32_t N, int32_t reduction, int32_t is_causal, void* stream_v) {
+  if (!acc || !out || B <= 0 || H <= 0 || M <= 0 || N <= 0)
+    return fail(FCR_ERR_BAD_ARG, "null pointer or non-positive size");
+  if (out_dtype != FCR_F16 && out_dtype != FCR_BF16 && out_dtype != FCR_F32)
+    return fail(FCR_ERR_BAD_ARG, "invalid out_dtype");
+  if (reduction != FCR_SUM && reduction != FCR_MEAN && reduction != FCR_MAX)
+    return fail(FCR_ERR_BAD_ARG, "invalid reduction code");
+  PassParams pp;
+  memset(&pp, 0, sizeof(pp));
+  pp.BH = B * H;
+  pp.N = N;
+  pp.M = M;
+  pp.out = out;
+  pp.out_dtype = out_dtype;
+  fill_mean(pp, reduction, is_causal, M, N);
+  const size_t total = (size_t)pp.BH * N;
+  const int blocks = (int)std::min<size_t>((total + 255) / 256, 4096);
+  finalize_kernel<<<blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream_v)>>>(acc, pp);
+  const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "finalize launch");
+  return FCR_OK;
+}
+
+int fcr_read_device_status(const void* workspace, void* stream_v, int32_t* code_out) {
+  if (!workspace) return fail(FCR_ERR_BAD_ARG, "null workspace");
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
+  int32_t words[4] = {0, 0, 0, 0};
+  cudaError_t e = cudaMemcpyAsync(words, workspace, sizeof(words), cudaMemcpyDeviceToHost, stream);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpyAsync(status)");
+  e = cudaStreamSynchronize(stream);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaStreamSynchronize");
+  if (code_out) *code_out = words[0];
+  if (words[0] != ST_OK)
+    return fail(FCR_ERR_DEVICE_TIMEOUT,
+                "device status " + std::to_string(words[0]) + " (block " + std::to_string(words[1]) +
+                    ", thread " + std::to_string(words[2]) + ", detail " + std::to_string(words[3]) +
+                    "): a bounded wait inside the kernel expired");
+  return FCR_OK;
+}
+
+int fcr_debug_scores(const fcr_problem* problem, const void* q, const void* k, float* scores,
+                     void* workspace, size_t workspace_bytes, void* stream_v) {
+  if (!problem || !q || !k || !scores) return fail(FCR_ERR_BAD_ARG, "null argument");
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
+  fcr_problem pr = *problem;
+  pr.is_causal = 0;
+  fcr_plan pl;
+  int rc = fcr_plan_problem(&pr, 0, &pl);
+  if (rc != FCR_OK) return rc;
+  rc = check_workspace(pl, workspace, workspace_bytes);
+  if (rc != FCR_OK) return rc;
+  uint8_t* ws = reinterpret_cast<uint8_t*>(workspace);
+  CUtensorMap map_q, map_k;
+  rc = make_tensor_map(&map_q, q, pr.in_dtype, pr.D, pr.M, pr.H, pr.B, pr.q_strides);
+  if (rc != FCR_OK) return rc;
+  rc = make_tensor_map(&map_k, k, pr.in_dtype, pr.D, pr.N, pr.H, pr.B, pr.k_strides);
+  if (rc != FCR_OK) return rc;
+  cudaError_t e = cudaMemsetAsync(ws + pl.off_status, 0, kStatusWords * 4, stream);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaMemsetAsync");
+  PassParams pp;
+  fill_common(pp, pr, pl, ws, false);
+  pp.n_split = 1;
+  pp.n_items = pp.BH * pl.row_blocks;
+  pp.dump = scores;
+  int sms = 0;
+  rc = device_sm_count(&sms);
+  if (rc != FCR_OK) return rc;
+  const int ctas = std::min(pp.n_items, sms);
+  return launch_pass_d<PH_DUMP, RED_SUM>(pl.d_pad, map_q, map_k, pp, ctas, stream);
+}
+
+double fcr_probe_ex2_rate(int32_t repeats) {
+  int sms = 0;
+  if (device_sm_count(&sms) != FCR_OK) return 0.0;
+  float* sink = nullptr;
+  if (cudaMalloc(&sink, 256) != cudaSuccess) return 0.0;
+  const int iters = 4096, threads = 1024, blocks = sms * 2;
+  cudaEvent_t a, b;
+  cudaEventCreate(&a);
+  cudaEventCreate(&b);
+  ex2_probe_kernel<<<blocks, threads>>>(sink, iters);
+  double best = 0.0;
+  for (int r = 0; r < std::max(repeats, 1); ++r) {
+    cudaEventRecord(a);
+    ex2_probe_kernel<<<blocks, threads>>>(sink, iters);
+    cudaEventRecord(b);
+    if (cudaEventSynchronize(b) != cudaSuccess) break;
+    float ms = 0.f;
+    cudaEventElapsedTime(&ms, a, b);
+    const double rate = (double)blocks * threads * 8.0 * iters / (ms * 1e-3);
+    best = std::max(best, rate);
+  }
+  cudaEventDestroy(a);
+  cudaEventDestroy(b);
+  cudaFree(sink);
+  return best;
+}
+
+}  // extern "C"

@@ -1,0 +1,255 @@
+// Host-side planner: validates a problem and derives the launch geometry and
+// workspace layout.  Pure C++ (no CUDA calls) so it can be exercised on a
+// machine without a GPU.  Takes the place of the grid computation of the
+// reference launcher (flash_colreduce/flash.py:286-287).
+#pragma once
+#include <stdint.h>
+
+#include <algorithm>
+#include <string>
+
+#include "../../include/flash_colreduce_b200.h"
+
+#if defined(__CUDACC__)
+#define FCR_HD __host__ __device__ __forceinline__
+#else
+#define FCR_HD inline
+#endif
+
+namespace fcr {
+
+constexpr int kTile = 128;            // rows per MMA tile (tensor-memory lanes)
+constexpr int kSubTiles = 2;          // stationary tiles a CTA owns
+constexpr int kBlockRows = kTile * kSubTiles;
+constexpr int kStatusWords = 64;
+
+// Geometry of one pass, shared by the host planner and the kernels.
+struct PassGeom {
+  int BH, H, M, N;
+  int LS;          // stationary length: M for the rows pass, N for the columns pass
+  int causal;
+  int off;         // query i attends keys j <= i + off
+  int n_sb;        // stationary blocks per head
+  int n_split;     // splits of the streamed range
+  int n_items;     // BH * n_sb * n_split
+  int sb_reverse;  // heaviest blocks first
+};
+
+// One work item: a head, a block of two stationary 128-row tiles, one split of
+// the streamed range.  Tiles [t_lo[a], t_hi[a]) are multiplied against
+// stationary sub-tile a; the item streams tiles [c_lo, c_hi).
+struct Item {
+  int bh, sp;
+  int r0[kSubTiles];
+  int t_lo[kSubTiles], t_hi[kSubTiles];
+  int c_lo, c_hi;
+};
+
+template <typename T>
+FCR_HD T hd_min(T a, T b) { return a < b ? a : b; }
+template <typename T>
+FCR_HD T hd_max(T a, T b) { return a > b ? a : b; }
+
+// Maps a linear work-item index to its head, stationary block and split, and
+// derives the streamed tile range of each stationary sub-tile.  The rows pass
+// keeps Q tiles stationary and streams the K tiles a tile's rows may attend;
+// the columns pass keeps K tiles stationary and streams the Q tiles that may
+// attend them.  Fully masked tiles are in no range (the reference skips them
+// per 64-row program, flash_colreduce/flash.py:201-207).
+template <bool COLS>
+FCR_HD Item decode_item(const PassGeom& p, int item) {
+  Item g;
+  const int sp = item % p.n_split;
+  const int rest = item / p.n_split;
+  const int o = rest % p.n_sb;
+  g.bh = rest / p.n_sb;
+  g.sp = sp;
+  const int sb = p.sb_reverse ? (p.n_sb - 1 - o) : o;
+  int lo = 0x7fffffff, hi = 0;
+  int tb[kSubTiles], te[kSubTiles];
+#if defined(__CUDACC__)
+#pragma unroll
+#endif
+  for (int a = 0; a < kSubTiles; ++a) {
+    const int r0 = (sb * kSubTiles + a) * kTile;
+    g.r0[a] = r0;
+    tb[a] = 0;
+    te[a] = 0;
+    if (r0 < p.LS) {
+      if (COLS) {
+        te[a] = (p.M + kTile - 1) / kTile;
+        if (p.causal) {
+          const int imin = hd_max(r0 - p.off, 0);  // first query that sees key r0
+          tb[a] = hd_min(imin / kTile, te[a]);
+        }
+      } else {
+        long long jmax = (long long)p.N - 1;
+        if (p.causal) {
+          const long long last_row = (long long)hd_min(r0 + kTile, p.M) - 1;
+          jmax = hd_min(jmax, last_row + p.off);
+        }
+        te[a] = (int)(jmax / kTile) + 1;
+      }
+      lo = hd_min(lo, tb[a]);
+      hi = hd_max(hi, te[a]);
+    }
+  }
+  if (lo > hi) lo = hi;
+  const long long len = hi - lo;
+  g.c_lo = lo + (int)((len * sp) / p.n_split);
+  g.c_hi = lo + (int)((len * (sp + 1)) / p.n_split);
+#if defined(__CUDACC__)
+#pragma unroll
+#endif
+  for (int a = 0; a < kSubTiles; ++a) {
+    g.t_lo[a] = hd_max(tb[a], g.c_lo);
+    g.t_hi[a] = hd_max(hd_min(te[a], g.c_hi), g.t_lo[a]);
+    if (g.r0[a] >= p.LS) {
+      g.t_lo[a] = g.c_lo;
+      g.t_hi[a] = g.c_lo;
+    }
+  }
+  return g;
+}
+
+inline int64_t ceil_div64(int64_t a, int64_t b) { return (a + b - 1) / b; }
+inline int64_t align_up64(int64_t a, int64_t b) { return ceil_div64(a, b) * b; }
+
+// Number of keys query row i attends (flash_colreduce/flash.py:22-27, naive.py:20-24).
+inline int64_t valid_keys(int64_t i, int64_t N, bool causal, int64_t off) {
+  if (!causal) return N;
+  return std::min<int64_t>(i + off + 1, N);
+}
+
+inline int choose_splits(int64_t base_items, int64_t max_len_tiles, int num_sms) {
+  // Split the streamed range until the grid covers the SMs about twice, never
+  // below one tile per chunk.
+  int s = 1;
+  while (base_items * s < 2LL * num_sms && 2LL * s <= max_len_tiles && s < 64) s *= 2;
+  return s;
+}
+
+inline int plan_problem(const fcr_problem& p, int num_sms, fcr_plan& pl, std::string& err) {
+  pl = fcr_plan{};
+  if (p.B <= 0 || p.H <= 0 || p.M <= 0 || p.N <= 0 || p.D <= 0) {
+    err = "B, H, M, N and D must all be positive";
+    return FCR_ERR_BAD_ARG;
+  }
+  if (p.reduction != FCR_SUM && p.reduction != FCR_MEAN && p.reduction != FCR_MAX) {
+    err = "invalid reduction code " + std::to_string(p.reduction);
+    return FCR_ERR_BAD_ARG;
+  }
+  if (p.in_dtype != FCR_F16 && p.in_dtype != FCR_BF16) {
+    err = "q and k must be fp16 or bf16 (dtype code " + std::to_string(p.in_dtype) + ")";
+    return FCR_ERR_UNSUPPORTED;
+  }
+  if (p.D > 128) {
+    err = "head dimension " + std::to_string(p.D) + " exceeds 128";
+    return FCR_ERR_UNSUPPORTED;
+  }
+  if (p.M > (1 << 30) || p.N > (1 << 30)) {
+    err = "M and N are limited to 2^30";
+    return FCR_ERR_UNSUPPORTED;
+  }
+  for (int t = 0; t < 2; ++t) {
+    const int64_t* s = t ? p.k_strides : p.q_strides;
+    const char* name = t ? "k" : "q";
+    if (s[3] != 1) {
+      err = std::string(name) + ": innermost stride must be 1";
+      return FCR_ERR_UNSUPPORTED;
+    }
+    const int32_t dims[3] = {p.B, p.H, t ? p.N : p.M};
+    for (int a = 0; a < 3; ++a) {
+      if (dims[a] > 1 && (s[a] <= 0 || s[a] % 8 != 0)) {
+        err = std::string(name) + ": stride " + std::to_string(a) + " = " + std::to_string(s[a]) +
+              " is not a positive multiple of 8 elements (16 bytes)";
+        return FCR_ERR_UNSUPPORTED;
+      }
+    }
+  }
+  if (num_sms <= 0) {
+    err = "num_sms must be positive";
+    return FCR_ERR_BAD_ARG;
+  }
+  const bool causal = p.is_causal != 0;
+  const int64_t off = !causal ? 0
+                      : (p.causal_offset >= 0 ? p.causal_offset
+                                              : std::max<int64_t>((int64_t)p.N - p.M, 0));
+  if (off > (1LL << 30)) {
+    err = "causal_offset too large";
+    return FCR_ERR_BAD_ARG;
+  }
+  const int64_t BH = (int64_t)p.B * p.H;
+
+  pl.d_pad = p.D <= 64 ? 64 : 128;
+  pl.rows_per_block = kBlockRows;
+  pl.m_pad = (int32_t)align_up64(p.M, kTile);
+  pl.n_pad = (int32_t)align_up64(p.N, kTile);
+  pl.causal_offset = off;
+  pl.row_blocks = (int32_t)ceil_div64(p.M, kBlockRows);
+  pl.col_blocks = (int32_t)ceil_div64(p.N, kBlockRows);
+
+  // Longest streamed range of any block, in tiles.
+  const int64_t keys_seen = causal ? std::min<int64_t>(p.N, (int64_t)p.M + off) : p.N;
+  const int64_t row_len = ceil_div64(keys_seen, kTile);
+  const int64_t col_len = ceil_div64(p.M, kTile);
+  pl.row_splits = choose_splits(BH * pl.row_blocks, row_len, num_sms);
+  pl.col_splits = choose_splits(BH * pl.col_blocks, col_len, num_sms);
+  const int64_t row_items = BH * pl.row_blocks * pl.row_splits;
+  const int64_t col_items = BH * pl.col_blocks * pl.col_splits;
+  if (row_items > (1LL << 30) || col_items > (1LL << 30)) {
+    err = "problem has too many work items";
+    return FCR_ERR_UNSUPPORTED;
+  }
+  pl.row_items = (int32_t)row_items;
+  pl.col_items = (int32_t)col_items;
+  pl.row_ctas = (int32_t)std::min<int64_t>(row_items, num_sms);
+  pl.col_ctas = (int32_t)std::min<int64_t>(col_items, num_sms);
+
+  int64_t scores = 0;
+  if (!causal) {
+    scores = (int64_t)p.M * p.N;
+  } else {
+    // rows i < N - off see i + off + 1 keys, the rest see N
+    const int64_t ramp = std::max<int64_t>(0, std::min<int64_t>(p.M, (int64_t)p.N - off));
+    scores = ramp * (off + 1) + ramp * (ramp - 1) / 2 + ((int64_t)p.M - ramp) * p.N;
+  }
+  pl.valid_scores = scores * BH;
+
+  int64_t o = 0;
+  pl.off_status = o;
+  o += align_up64(kStatusWords * 4, 256);
+  pl.off_neg_lse = o;
+  o += align_up64(BH * pl.m_pad * 4, 256);
+  if (pl.row_splits > 1) {
+    pl.off_part_m = o;
+    o += align_up64((int64_t)pl.row_splits * BH * pl.m_pad * 4, 256);
+    pl.off_part_l = o;
+    o += align_up64((int64_t)pl.row_splits * BH * pl.m_pad * 4, 256);
+  }
+  if (pl.col_splits > 1) {
+    pl.off_part_out = o;
+    o += align_up64((int64_t)pl.col_splits * BH * pl.n_pad * 4, 256);
+  }
+  pl.workspace_bytes = o;
+  return FCR_OK;
+}
+
+// Geometry of the rows pass (cols == false) or the columns pass of a plan.
+inline PassGeom pass_geometry(const fcr_problem& p, const fcr_plan& pl, bool cols) {
+  PassGeom g{};
+  g.BH = p.B * p.H;
+  g.H = p.H;
+  g.M = p.M;
+  g.N = p.N;
+  g.causal = p.is_causal ? 1 : 0;
+  g.off = (int)pl.causal_offset;
+  g.LS = cols ? p.N : p.M;
+  g.n_sb = cols ? pl.col_blocks : pl.row_blocks;
+  g.n_split = cols ? pl.col_splits : pl.row_splits;
+  g.n_items = cols ? pl.col_items : pl.row_items;
+  g.sb_reverse = (!cols && g.causal) ? 1 : 0;  // rows pass: late blocks see the most keys
+  return g;
+}
+
+}  // namespace fcr

@@ -1,0 +1,178 @@
+"""``flash_colreduce`` -- the public operator, backed by the sm_100a library.
+
+Same signature, semantics, output shape/dtype and error messages as the
+reference operator (flash_colreduce/flash.py:311-385).  All device work is
+done by hand-written CUDA kernels reached through the C ABI; there is no
+Triton path and no CPU or eager fallback.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+import os
+from typing import Optional
+
+import torch
+
+from . import _native as nat
+
+__all__ = ["flash_colreduce", "colreduce_partial", "finalize_scores", "valid_scores"]
+
+_DTYPE_CODES = {torch.float16: nat.FCR_F16, torch.bfloat16: nat.FCR_BF16, torch.float32: nat.FCR_F32}
+
+
+def _debug_sync() -> bool:
+    return os.environ.get("FCR_DEBUG_SYNC", "0") not in ("", "0")
+
+
+def _tma_ready(x: torch.Tensor) -> torch.Tensor:
+    """Returns ``x`` or a copy whose layout a TMA tensor map can describe.
+
+    Needed: innermost stride 1, every other stride of a dimension longer than
+    one a positive multiple of 8 elements (16 bytes), 16-byte aligned base.
+    The head dimension is zero-padded to a multiple of 8 when it is not one,
+    which changes no dot product (the reference pads to a power of two for the
+    same reason, flash_colreduce/flash.py:368-373).
+    """
+    d = x.shape[-1]
+    if d % 8 != 0:
+        x = torch.nn.functional.pad(x, (0, 8 - d % 8))
+    ok = x.stride(3) == 1 and x.data_ptr() % 16 == 0
+    for dim in range(3):
+        if x.shape[dim] > 1 and (x.stride(dim) <= 0 or x.stride(dim) % 8 != 0):
+            ok = False
+    return x if ok else x.contiguous()
+
+
+def _launch(query, key, out, out_code, reduction_code, is_causal, scale, causal_offset, mean_M, mean_N):
+    b, h, m, _ = query.shape
+    n = key.shape[2]
+    q = _tma_ready(query)
+    k = _tma_ready(key)
+    d = q.shape[-1]
+    prob = nat.make_problem(b, h, m, n, d, q.stride(), k.stride(), _DTYPE_CODES[q.dtype],
+                            reduction_code, is_causal, scale, causal_offset, mean_M, mean_N)
+    with torch.cuda.device(q.device):
+        pl = nat.plan(prob, 0)
+        ws = torch.empty(int(pl.workspace_bytes), dtype=torch.uint8, device=q.device)
+        stream = torch.cuda.current_stream(q.device).cuda_stream
+        rc = nat.lib.fcr_colreduce(C.byref(prob), q.data_ptr(), k.data_ptr(), out.data_ptr(), out_code,
+                                   ws.data_ptr(), ws.numel(), stream)
+        nat.check(rc, "fcr_colreduce")
+        if _debug_sync():
+            nat.check(nat.lib.fcr_read_device_status(ws.data_ptr(), stream, None), "fcr_colreduce (device)")
+    return out
+
+
+def _validate(query: torch.Tensor, key: torch.Tensor, reduction: str) -> None:
+    if not query.is_cuda or not key.is_cuda:
+        raise ValueError("Query and key tensors must be on CUDA device.")
+    if not all(query.shape[i] == key.shape[i] for i in [0, 1, 3]):
+        raise ValueError(
+            f"Query and key tensors must have same batch size, number of heads, and head dimension. "
+            f"Got query shape: {query.shape}, key shape: {key.shape}."
+        )
+    if reduction not in ["sum", "mean", "max"]:
+        raise ValueError(f"Invalid reduction: {reduction}. Must be 'sum', 'mean', or 'max'.")
+    if query.dtype != key.dtype or query.dtype not in (torch.float16, torch.bfloat16):
+        raise TypeError(
+            f"flash_colreduce runs fp16 or bf16 tensor-core kernels; got query {query.dtype}, key {key.dtype}."
+        )
+    if query.shape[-1] > 128:
+        raise ValueError(f"Head dimension {query.shape[-1]} exceeds 128, the largest the sm_100a kernels take.")
+
+
+def flash_colreduce(
+    query: torch.Tensor,
+    key: torch.Tensor,
+    reduction: str,
+    is_causal: bool = False,
+    scale: Optional[float] = None,
+) -> torch.Tensor:
+    """Column reduction of the softmax attention matrix, never materialised.
+
+    ``S = softmax(Q K^T * scale)`` per (batch, head) and query row;
+    ``R[b, h, n] = reduce_m S[b, h, m, n]`` with ``reduce`` one of ``"sum"``,
+    ``"mean"``, ``"max"``.  With ``is_causal`` the mask is right-aligned:
+    query ``m`` attends keys up to ``m + max(N - M, 0)``; ``"mean"`` divides a
+    column by the number of queries the reference counts for it
+    (flash_colreduce/flash.py:377-384: ``M`` for the first ``max(N - M, 0)``
+    columns, then ``N - n``).
+
+    Args:
+        query: (B, H, M, D) fp16 or bf16 CUDA tensor.
+        key: (B, H, N, D), same dtype and device.
+        reduction: "sum", "mean" or "max".
+        is_causal: apply the right-aligned causal mask.
+        scale: softmax scale, default ``1 / sqrt(D)``.
+
+    Returns:
+        (B, H, N) tensor of ``query.dtype``.  Accumulation is fp32 and the
+        result is rounded once; run-to-run results are bitwise identical.
+    """
+    _validate(query, key, reduction)
+    b, h, m, d = query.shape
+    n = key.shape[2]
+    if scale is None:
+        scale = 1 / math.sqrt(d)
+    out = torch.empty((b, h, n), dtype=query.dtype, device=query.device)
+    if out.numel() == 0:
+        return out
+    if m == 0:
+        # no query contributes: zeros for sum / max, 0/0 for mean as in the reference
+        out.zero_()
+        return out / 0 if reduction == "mean" else out
+    return _launch(query, key, out, _DTYPE_CODES[out.dtype], nat.REDUCTION_CODES[reduction], is_causal,
+                   scale, -1, 0, 0)
+
+
+def colreduce_partial(
+    query: torch.Tensor,
+    key: torch.Tensor,
+    reduction: str,
+    is_causal: bool,
+    scale: float,
+    causal_offset: int,
+) -> torch.Tensor:
+    """fp32 column sums (``"sum"``) or maxima (``"max"``) of a row slice.
+
+    ``query`` holds a slice of the rows of a larger problem; row ``i`` of the
+    slice attends keys ``j <= i + causal_offset``.  No mean divisor, no cast:
+    shards are combined with ``+`` / ``max`` and passed to
+    :func:`finalize_scores`.  Used by the multi-GPU driver.
+    """
+    _validate(query, key, reduction)
+    if reduction == "mean":
+        raise ValueError("colreduce_partial takes 'sum' or 'max'; apply the mean in finalize_scores")
+    b, h, m, _ = query.shape
+    n = key.shape[2]
+    out = torch.empty((b, h, n), dtype=torch.float32, device=query.device)
+    if out.numel() == 0 or m == 0:
+        return out.zero_()
+    return _launch(query, key, out, nat.FCR_F32, nat.REDUCTION_CODES[reduction], is_causal, scale,
+                   causal_offset if is_causal else -1, 0, 0)
+
+
+def finalize_scores(acc: torch.Tensor, m: int, reduction: str, is_causal: bool, dtype: torch.dtype) -> torch.Tensor:
+    """Mean divisor (flash_colreduce/flash.py:377-384) and cast of fp32 (B,H,N) sums / maxima."""
+    if acc.dtype != torch.float32 or not acc.is_cuda or not acc.is_contiguous():
+        raise ValueError("acc must be a contiguous fp32 CUDA tensor")
+    b, h, n = acc.shape
+    out = torch.empty((b, h, n), dtype=dtype, device=acc.device)
+    if out.numel() == 0:
+        return out
+    with torch.cuda.device(acc.device):
+        stream = torch.cuda.current_stream(acc.device).cuda_stream
+        rc = nat.lib.fcr_finalize(acc.data_ptr(), out.data_ptr(), _DTYPE_CODES[dtype], b, h, m, n,
+                                  nat.REDUCTION_CODES[reduction], 1 if is_causal else 0, stream)
+        nat.check(rc, "fcr_finalize")
+    return out
+
+
+def valid_scores(b: int, h: int, m: int, n: int, is_causal: bool) -> int:
+    """Number of unmasked attention scores of a problem: the unit of the throughput metric."""
+    if not is_causal:
+        return b * h * m * n
+    off = max(n - m, 0)
+    ramp = max(0, min(m, n - off))
+    return b * h * (ramp * (off + 1) + ramp * (ramp - 1) // 2 + (m - ramp) * n)

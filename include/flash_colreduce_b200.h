@@ -1,0 +1,185 @@
+/*
+ * flash_colreduce_b200 -- C ABI of the sm_100a column-reduction library.
+ *
+ * The library computes, for queries Q (B,H,M,D) and keys K (B,H,N,D),
+ *
+ *     P[b,h,i,:] = softmax_j( Q[b,h,i,:] . K[b,h,j,:] * scale  (+ right-aligned causal mask) )
+ *     R[b,h,j]   = reduce_i P[b,h,i,j]            reduce in {sum, mean, max}
+ *
+ * without materialising the (B,H,M,N) matrix.  Every entry point takes plain
+ * pointers and sizes; device pointers are raw CUDA addresses, `stream` is a
+ * `cudaStream_t` passed as `void*`.  All launches are asynchronous on that
+ * stream and the library never synchronises, except where a function says so.
+ *
+ * Every function returning `int` returns an fcr_status; a human-readable
+ * message for the calling thread's last failure is available from
+ * fcr_last_error().  No C++ exception crosses this boundary.
+ *
+ * Reference interfaces replaced (paths inside z-lab/flash-colreduce v0.2.2):
+ *   flash_colreduce/flash.py:277-308  `_flash_colreduce`   -> fcr_colreduce
+ *   flash_colreduce/flash.py:144-274  `_flash_colreduce_kernel` (Triton) -> the kernels behind fcr_colreduce
+ *   flash_colreduce/flash.py:377-385  mean divisor + cast  -> fused into fcr_colreduce; fcr_finalize for sharded runs
+ */
+#ifndef FLASH_COLREDUCE_B200_H_
+#define FLASH_COLREDUCE_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum fcr_status {
+  FCR_OK = 0,
+  FCR_ERR_BAD_ARG = 1,        /* null pointer, negative size, inconsistent problem */
+  FCR_ERR_UNSUPPORTED = 2,    /* shape / dtype / stride the sm_100a kernels cannot take */
+  FCR_ERR_WORKSPACE = 3,      /* workspace missing, misaligned or smaller than fcr_workspace_bytes() */
+  FCR_ERR_DEVICE_TIMEOUT = 4, /* a bounded device-side wait expired; see fcr_read_device_status */
+  FCR_ERR_CUDA = 5            /* a CUDA runtime / driver call failed */
+} fcr_status;
+
+typedef enum fcr_dtype { FCR_F16 = 0, FCR_BF16 = 1, FCR_F32 = 2 } fcr_dtype;
+typedef enum fcr_reduction { FCR_SUM = 0, FCR_MEAN = 1, FCR_MAX = 2 } fcr_reduction;
+
+/*
+ * One column-reduction problem.  Strides are in ELEMENTS, in (B,H,rows,D)
+ * order, exactly the four numbers `tensor.stride()` returns; the innermost
+ * stride must be 1 and the other three must be multiples of 8 elements
+ * (16 bytes) -- a TMA tensor-map requirement.
+ *
+ * Replaces the argument list of `_flash_colreduce_kernel`
+ * (flash_colreduce/flash.py:145-167: pointers, scale, eight strides, H, M, N,
+ * D, REDUCTION, CAUSAL).
+ */
+typedef struct fcr_problem {
+  int32_t B, H, M, N, D;
+  int64_t q_strides[4];
+  int64_t k_strides[4];
+  int32_t in_dtype;      /* fcr_dtype of q and k: FCR_F16 or FCR_BF16 */
+  int32_t reduction;     /* fcr_reduction */
+  int32_t is_causal;     /* 0 / 1 */
+  float scale;           /* softmax scale applied to q.k (the reference's default is 1/sqrt(D)) */
+  /*
+   * Causal alignment: query row i attends keys j <= i + causal_offset.
+   * A negative value selects the reference's right alignment max(N - M, 0)
+   * (flash_colreduce/flash.py:202, naive.py:21).  A row-sliced shard of a
+   * larger problem passes the offset of its first row explicitly.
+   */
+  int64_t causal_offset;
+  /*
+   * Divisor rule for FCR_MEAN (flash_colreduce/flash.py:377-384): the rule is
+   * evaluated with these "whole problem" row/key counts.  0 selects M / N of
+   * this problem.
+   */
+  int32_t mean_M, mean_N;
+} fcr_problem;
+
+/* Launch plan derived on the host from a problem and an SM count. */
+typedef struct fcr_plan {
+  int32_t d_pad;            /* head dimension the kernels run at: 64 or 128 (zero-filled by TMA) */
+  int32_t rows_per_block;   /* stationary rows a CTA owns: 256 */
+  int32_t m_pad, n_pad;     /* M and N rounded up to 128 */
+  int32_t row_blocks;       /* phase 1: blocks of query rows per head */
+  int32_t col_blocks;       /* phase 2: blocks of key columns per head */
+  int32_t row_splits;       /* phase 1: splits of the key range per row block */
+  int32_t col_splits;       /* phase 2: splits of the query range per column block */
+  int32_t row_items, col_items; /* work items per phase = B*H*blocks*splits */
+  int32_t row_ctas, col_ctas;   /* persistent CTAs launched per phase */
+  int64_t causal_offset;    /* resolved offset */
+  int64_t valid_scores;     /* B*H*sum_i valid(i): the unit the throughput metric counts */
+  /* workspace layout, byte offsets from the workspace base */
+  int64_t off_status;       /* int32[64] device status words */
+  int64_t off_neg_lse;      /* float[B*H][m_pad]: minus the base-2 log-sum-exp of each query row */
+  int64_t off_part_m;       /* float[row_splits][B*H][m_pad] running maxima (row_splits > 1) */
+  int64_t off_part_l;       /* float[row_splits][B*H][m_pad] running sums   (row_splits > 1) */
+  int64_t off_part_out;     /* float[col_splits][B*H][n_pad] column partials (col_splits > 1) */
+  int64_t workspace_bytes;
+} fcr_plan;
+
+/* Library version string, e.g. "0.1.0". */
+const char* fcr_version(void);
+
+/* Message describing the last failure on the calling thread ("" if none). */
+const char* fcr_last_error(void);
+
+/*
+ * Pure host function: validates `problem` and fills `plan` for a device with
+ * `num_sms` streaming multiprocessors (pass 0 to query the current CUDA
+ * device).  Replaces the grid computation of flash_colreduce/flash.py:287.
+ */
+int fcr_plan_problem(const fcr_problem* problem, int32_t num_sms, fcr_plan* plan);
+
+/*
+ * Pure host function: decodes work item `item` of pass 1 (rows pass: Q tiles
+ * stationary, K tiles streamed) or pass 2 (columns pass: K tiles stationary,
+ * Q tiles streamed) with the same routine the kernels run.  out[10] receives
+ * {head, split, chunk_lo, chunk_hi, row0_a, tile_lo_a, tile_hi_a, row0_b,
+ * tile_lo_b, tile_hi_b}: 128-row streamed tiles [tile_lo, tile_hi) are
+ * multiplied against the stationary tile starting at row0.  This is the
+ * counterpart of the per-program loop bounds of flash_colreduce/flash.py:201-207.
+ */
+int fcr_plan_item(const fcr_problem* problem, const fcr_plan* plan, int32_t pass, int32_t item,
+                  int32_t* out);
+
+/*
+ * Bytes of device workspace fcr_colreduce needs for `problem` (0 on error).
+ * The reference allocates its fp32 accumulator itself
+ * (flash_colreduce/flash.py:286); here the caller owns every allocation.
+ */
+size_t fcr_workspace_bytes(const fcr_problem* problem, int32_t num_sms);
+
+/*
+ * The operator.  q, k: device pointers to the first element of the (B,H,*,D)
+ * tensors described by `problem`.  out: device pointer to a contiguous
+ * (B,H,N) tensor of `out_dtype`.  workspace: device memory, 256-byte aligned,
+ * at least fcr_workspace_bytes() long; its contents need not be initialised.
+ * Results are deterministic: no atomics, fixed summation order.
+ *
+ * With reduction == FCR_MEAN the divisor of flash_colreduce/flash.py:377-384
+ * is applied in fp32 before the single rounding to `out_dtype`.
+ *
+ * Replaces `_flash_colreduce` (flash_colreduce/flash.py:277-308) together
+ * with the tail of `flash_colreduce` (flash.py:377-385).
+ */
+int fcr_colreduce(const fcr_problem* problem, const void* q, const void* k, void* out,
+                  int32_t out_dtype, void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * Tail of a sharded run: `acc` holds fp32 column sums (or maxima) of shape
+ * (B,H,N) that were produced with reduction FCR_SUM / FCR_MAX and combined
+ * across shards; this applies the mean divisor (for FCR_MEAN) for a whole
+ * problem of M rows and N keys and casts to `out_dtype`.
+ * Replaces flash_colreduce/flash.py:377-385 for that case.
+ */
+int fcr_finalize(const float* acc, void* out, int32_t out_dtype, int32_t B, int32_t H, int32_t M,
+                 int32_t N, int32_t reduction, int32_t is_causal, void* stream);
+
+/*
+ * Synchronises `stream` and reads the device status words of a workspace
+ * used by fcr_colreduce.  Returns FCR_OK if no bounded wait expired, else
+ * FCR_ERR_DEVICE_TIMEOUT with details in fcr_last_error(); `code_out` (may be
+ * NULL) receives the raw first status word.
+ */
+int fcr_read_device_status(const void* workspace, void* stream, int32_t* code_out);
+
+/*
+ * Bring-up diagnostic: writes the raw fp32 scores Q.K^T (no scale, no mask)
+ * of every head into `scores`, a (B*H, m_pad, n_pad) fp32 device array, using
+ * the same TMA / tcgen05 / tensor-memory pipeline as the operator.  Meant for
+ * small problems only.
+ */
+int fcr_debug_scores(const fcr_problem* problem, const void* q, const void* k, float* scores,
+                     void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * Measurement helper: runs a register-only ex2.approx.ftz.f32 loop on every
+ * SM and returns the sustained rate in exponentials per second (the MUFU
+ * bound of the roofline).  Synchronises the device.  Returns 0 on error.
+ */
+double fcr_probe_ex2_rate(int32_t repeats);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FLASH_COLREDUCE_B200_H_ */
