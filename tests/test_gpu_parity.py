@@ -1,0 +1,234 @@
+"""Parity of the sm_100a kernels with the oracle and the reference's outputs (needs a B200)."""
+import math
+import os
+
+import pytest
+import torch
+
+from conftest import assert_parity
+from oracle import oracle_colreduce
+
+pytestmark = pytest.mark.gpu
+
+os.environ.setdefault("FCR_DEBUG_SYNC", "1")  # read the device status words after every call
+
+
+def _dev():
+    assert torch.cuda.is_available(), "these tests need a CUDA device"
+    return torch.device("cuda:0")
+
+
+def _f32(q, k, red, causal, scale=None):
+    """The operator with an fp32 result (mean included): the kernels' accumulators, unrounded."""
+    from flash_colreduce_b200 import _native as nat
+    from flash_colreduce_b200 import op
+
+    if scale is None:
+        scale = 1 / math.sqrt(q.shape[-1])
+    out = torch.empty(q.shape[0], q.shape[1], k.shape[2], dtype=torch.float32, device=q.device)
+    return op._launch(q, k, out, nat.FCR_F32, nat.REDUCTION_CODES[red], causal, scale, -1, 0, 0)
+
+
+def _rand(shape, seed, dtype=torch.float16):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randn(*shape, generator=g, dtype=torch.float32).to(dtype)
+
+
+def test_native_library_is_loaded():
+    from flash_colreduce_b200 import _native as nat
+
+    assert nat.lib.fcr_version().decode() == "0.1.0"
+    assert nat.lib.fcr_probe_ex2_rate(1) > 1e12
+
+
+def test_golden_vectors_fp32(golden):
+    """Every output of the reference's naive_colreduce stored in tests/golden/."""
+    dev = _dev()
+    for name, red, causal in golden.cases():
+        q, k, scale = golden.inputs(name)
+        got = _f32(q.to(dev), k.to(dev), red, causal, scale)
+        assert_parity(got, golden.output(name, red, causal), red)
+
+
+def test_golden_vectors_api_dtype(golden):
+    from flash_colreduce_b200 import flash_colreduce
+
+    dev = _dev()
+    for name, red, causal in golden.cases():
+        q, k, scale = golden.inputs(name)
+        got = flash_colreduce(q.to(dev), k.to(dev), red, is_causal=causal, scale=scale)
+        assert got.dtype == torch.float16 and got.shape == golden.output(name, red, causal).shape
+        assert_parity(got, golden.output(name, red, causal), red, extra_rtol=2.0 ** -11)
+
+
+# The reference's test matrix (tests/test_correctness.py:8-13): 720 cases.
+@pytest.mark.parametrize("d", [16, 32, 64, 48, 72])
+@pytest.mark.parametrize("m,n", [(128, 128), (131, 131), (128, 1024), (131, 1027)])
+def test_reference_matrix(m, n, d):
+    from flash_colreduce_b200 import flash_colreduce
+
+    dev = _dev()
+    for b in (1, 4, 7):
+        for h in (8, 13):
+            q = _rand((b, h, m, d), 0)
+            k = _rand((b, h, n, d), 1)
+            qd, kd = q.to(dev), k.to(dev)
+            for red in ("sum", "mean", "max"):
+                for causal in (False, True):
+                    want = oracle_colreduce(q, k, red, causal)
+                    assert_parity(_f32(qd, kd, red, causal), want, red)
+                    out = flash_colreduce(qd, kd, reduction=red, is_causal=causal)
+                    # the reference's own bar for the fp16 result: atol = rtol = 1e-3
+                    torch.testing.assert_close(out.float().cpu(), want, atol=1e-3, rtol=1e-3)
+
+
+@pytest.mark.parametrize("red", ["sum", "mean", "max"])
+def test_config_nonsquare_batch(red):
+    """B=8, H=16, M=N=512, d=64, not causal."""
+    dev = _dev()
+    q, k = _rand((8, 16, 512, 64), 0), _rand((8, 16, 512, 64), 1)
+    assert_parity(_f32(q.to(dev), k.to(dev), red, False), oracle_colreduce(q, k, red, False), red)
+
+
+@pytest.mark.parametrize("red", ["sum", "mean", "max"])
+def test_config_decode(red):
+    """q (1,32,128,128), k (1,32,4096,128), right-aligned causal mask."""
+    dev = _dev()
+    q, k = _rand((1, 32, 128, 128), 0), _rand((1, 32, 4096, 128), 1)
+    assert_parity(_f32(q.to(dev), k.to(dev), red, True), oracle_colreduce(q, k, red, True), red)
+
+
+def _vlm_inputs(b, h, n, d, seed):
+    """Attention-sink keys 0-3 scaled by 8; keys 512-6655 drawn with standard deviation 0.5."""
+    q = _rand((b, h, n, d), seed).float()
+    k = _rand((b, h, n, d), seed + 1).float()
+    k[:, :, 0:4] *= 8
+    k[:, :, 512:6656] *= 0.5
+    return q.half(), k.half()
+
+
+def test_config_vlm_pruning_heads():
+    """Three heads of the B=4, H=32, M=N=8192, d=128 causal mean configuration."""
+    dev = _dev()
+    q, k = _vlm_inputs(1, 3, 8192, 128, 10)
+    for red in ("mean", "sum", "max"):
+        assert_parity(_f32(q.to(dev), k.to(dev), red, True), oracle_colreduce(q, k, red, True), red)
+
+
+def test_long_context_properties():
+    """M=N=131072, d=128, causal: checked through size-independent properties and row slices."""
+    from flash_colreduce_b200 import colreduce_partial
+
+    dev = _dev()
+    n, d, h = 131072, 128, 2
+    q, k = _rand((1, h, n, d), 20), _rand((1, h, n, d), 21)
+    qd, kd = q.to(dev), k.to(dev)
+    scale = 1 / math.sqrt(d)
+    total = _f32(qd, kd, "sum", True)
+    # every softmax row sums to one, so the column sums add up to the number of rows
+    torch.testing.assert_close(total.double().sum(dim=-1).cpu(), torch.full((1, h), float(n), dtype=torch.float64),
+                               rtol=1e-4, atol=0)
+    again = _f32(qd, kd, "sum", True)
+    assert torch.equal(total, again), "summation order must be fixed"
+    mx = _f32(qd, kd, "max", True)
+    assert float(mx.max()) <= 1.0 + 1e-6 and float(mx.min()) > 0.0
+    assert bool((mx <= total + 1e-6).all())
+    assert float(mx[..., -1].min()) == pytest.approx(float(total[..., -1].min()))  # last key: one query
+    # row slices against the oracle: first rows, a slice across the middle, the last rows
+    acc = torch.zeros_like(total)
+    for lo, hi in ((0, 384), (65500, 65800), (n - 300, n)):
+        part = colreduce_partial(qd[:, :, lo:hi], kd[:, :, :hi], "sum", True, scale, causal_offset=lo)
+        want = oracle_colreduce(q, k[:, :, :hi], "sum", True, scale, row_range=(lo, hi))
+        # oracle_colreduce aligns the mask for an (n x hi) problem: rows see keys <= i + max(hi - n, 0) = i
+        assert_parity(part, want, "sum")
+        acc[..., :hi] += part
+    assert bool((acc <= total * (1 + 1e-4) + 1e-6).all())
+
+
+def test_masked_positions_are_exact_zero():
+    """Keys no query of a slice may attend must come out as 0.0 exactly."""
+    from flash_colreduce_b200 import colreduce_partial
+
+    dev = _dev()
+    q, k = _rand((1, 2, 300, 64), 3), _rand((1, 2, 300, 64), 4)
+    k[:, :, 200:] *= 30  # would dominate every softmax if the mask leaked
+    for red in ("sum", "max"):
+        got = colreduce_partial(q[:, :, :70].to(dev), k.to(dev), red, True, 0.125, causal_offset=0)
+        assert bool((got[..., 70:] == 0).all())
+        want = oracle_colreduce(q, k, red, True, 0.125, row_range=(0, 70))
+        assert_parity(got, want, red)
+
+
+@pytest.mark.parametrize("m,n", [(300, 100), (1000, 257), (1, 500), (129, 128)])
+def test_more_queries_than_keys_and_edge_shapes(m, n):
+    dev = _dev()
+    q, k = _rand((2, 3, m, 64), 5), _rand((2, 3, n, 64), 6)
+    for red in ("sum", "mean", "max"):
+        for causal in (False, True):
+            assert_parity(_f32(q.to(dev), k.to(dev), red, causal), oracle_colreduce(q, k, red, causal), red)
+
+
+@pytest.mark.parametrize("scale", [0.3, -0.2, 1.5])
+def test_user_scale(scale):
+    dev = _dev()
+    q, k = _rand((1, 2, 200, 32), 7), _rand((1, 2, 333, 32), 8)
+    for red in ("sum", "max"):
+        assert_parity(_f32(q.to(dev), k.to(dev), red, True, scale), oracle_colreduce(q, k, red, True, scale), red)
+
+
+def test_bfloat16_inputs():
+    from flash_colreduce_b200 import flash_colreduce
+
+    dev = _dev()
+    q, k = _rand((1, 2, 260, 128), 9, torch.bfloat16), _rand((1, 2, 400, 128), 10, torch.bfloat16)
+    for red in ("sum", "mean", "max"):
+        want = oracle_colreduce(q, k, red, True)
+        assert_parity(_f32(q.to(dev), k.to(dev), red, True), want, red)
+        out = flash_colreduce(q.to(dev), k.to(dev), red, is_causal=True)
+        assert out.dtype == torch.bfloat16
+        assert_parity(out, want, red, extra_rtol=2.0 ** -8)
+
+
+def test_strided_and_odd_inputs():
+    """Row slices, (B,M,H,D) storage, and a head dimension that is not a multiple of 8."""
+    dev = _dev()
+    q, k = _rand((2, 4, 500, 64), 11), _rand((2, 4, 700, 64), 12)
+    qd, kd = q.to(dev), k.to(dev)
+    got = _f32(qd[:, :, 100:400], kd, "sum", False)
+    assert_parity(got, oracle_colreduce(q[:, :, 100:400], k, "sum", False), "sum")
+    q_bmhd = qd.permute(0, 2, 1, 3).contiguous().permute(0, 2, 1, 3)  # logical (B,H,M,D), memory (B,M,H,D)
+    assert not q_bmhd.is_contiguous()
+    assert_parity(_f32(q_bmhd, kd, "mean", True), oracle_colreduce(q, k, "mean", True), "mean")
+    q2, k2 = _rand((1, 2, 150, 20), 13), _rand((1, 2, 90, 20), 14)
+    assert_parity(_f32(q2.to(dev), k2.to(dev), "max", True), oracle_colreduce(q2, k2, "max", True), "max")
+
+
+def test_errors_match_the_reference_messages():
+    from flash_colreduce_b200 import flash_colreduce
+
+    dev = _dev()
+    q = torch.zeros(1, 2, 8, 16, dtype=torch.float16, device=dev)
+    with pytest.raises(ValueError, match="must be on CUDA device"):
+        flash_colreduce(q.cpu(), q, "sum")
+    with pytest.raises(ValueError, match="same batch size, number of heads, and head dimension"):
+        flash_colreduce(q, torch.zeros(1, 3, 8, 16, dtype=torch.float16, device=dev), "sum")
+    with pytest.raises(ValueError, match="Invalid reduction: prod"):
+        flash_colreduce(q, q, "prod")
+    with pytest.raises(TypeError):
+        flash_colreduce(q.float(), q.float(), "sum")
+    assert flash_colreduce(q[:, :, :0], q, "sum").shape == (1, 2, 8)
+    assert flash_colreduce(q, q[:, :, :0], "sum").shape == (1, 2, 0)
+
+
+def test_runs_on_the_current_stream_without_sync():
+    from flash_colreduce_b200 import flash_colreduce
+
+    dev = _dev()
+    q, k = _rand((1, 4, 512, 64), 15).to(dev), _rand((1, 4, 512, 64), 16).to(dev)
+    base = flash_colreduce(q, k, "sum")
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        other = flash_colreduce(q, k, "sum")
+    s.synchronize()
+    assert torch.equal(base, other)
