@@ -5,8 +5,10 @@ Drop-in for the Python API of z-lab/flash-colreduce
 and ``__version__``.
 """
 from .dense import naive_colreduce
+from .host import flash_colreduce_host
 from .op import colreduce_partial, finalize_scores, flash_colreduce, valid_scores
 
 __version__ = "0.1.0"
 __all__ = ["flash_colreduce", "naive_colreduce", "colreduce_partial", "finalize_scores", "valid_scores",
+           "flash_colreduce_host",
            "__version__"]

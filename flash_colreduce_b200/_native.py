@@ -30,6 +30,9 @@ EXPORTS = (
     "fcr_colreduce",
     "fcr_finalize",
     "fcr_read_device_status",
+    "fcr_trace_enable",
+    "fcr_trace_count",
+    "fcr_trace_read",
     "fcr_debug_scores",
     "fcr_probe_ex2_rate",
 )
@@ -93,6 +96,12 @@ def _load() -> C.CDLL:
     lib.fcr_finalize.restype = C.c_int
     lib.fcr_read_device_status.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(C.c_int32)]
     lib.fcr_read_device_status.restype = C.c_int
+    lib.fcr_trace_enable.argtypes = [C.c_int32]
+    lib.fcr_trace_enable.restype = C.c_int
+    lib.fcr_trace_count.argtypes = []
+    lib.fcr_trace_count.restype = C.c_int32
+    lib.fcr_trace_read.argtypes = [C.c_int32, C.POINTER(C.c_float), C.POINTER(C.c_float)]
+    lib.fcr_trace_read.restype = C.c_int
     lib.fcr_debug_scores.argtypes = [C.POINTER(Problem), C.c_void_p, C.c_void_p, C.c_void_p,
                                      C.c_void_p, C.c_size_t, C.c_void_p]
     lib.fcr_debug_scores.restype = C.c_int
@@ -142,3 +151,13 @@ def plan_item(problem: Problem, pl: Plan, which_pass: int, item: int) -> dict:
     v = list(buf)
     return {"head": v[0], "split": v[1], "chunk": (v[2], v[3]),
             "sub": [(v[4], v[5], v[6]), (v[7], v[8], v[9])]}
+
+
+def trace_times() -> list:
+    """(rows_ms, cols_ms) of every call traced since ``fcr_trace_enable(1)``; synchronises."""
+    out = []
+    for i in range(lib.fcr_trace_count()):
+        a, b = C.c_float(0), C.c_float(0)
+        check(lib.fcr_trace_read(i, C.byref(a), C.byref(b)), "fcr_trace_read")
+        out.append((a.value, b.value))
+    return out

@@ -32,8 +32,9 @@
 #include <stdio.h>
 #include <string.h>
 
-#include <mutex>
+#include <array>
 #include <string>
+#include <vector>
 
 #include "plan.h"
 #include "ptx_sm100.cuh"
@@ -576,6 +577,34 @@ __global__ void ex2_probe_kernel(float* sink, int iters) {
 // ===================================================================== host
 static thread_local std::string g_last_error;
 
+// Per-thread trace: CUDA events recorded around the two passes of each call.
+struct Trace {
+  bool on = false;
+  int used = 0;
+  std::vector<std::array<cudaEvent_t, 3>> events;
+};
+static thread_local Trace g_trace;
+
+static cudaEvent_t trace_event(int which) {
+  if (!g_trace.on) return nullptr;
+  if (which == 0) {
+    if (g_trace.used >= 256) return nullptr;
+    if ((int)g_trace.events.size() <= g_trace.used) {
+      std::array<cudaEvent_t, 3> e{};
+      for (auto& ev : e)
+        if (cudaEventCreate(&ev) != cudaSuccess) return nullptr;
+      g_trace.events.push_back(e);
+    }
+  }
+  if (g_trace.used >= (int)g_trace.events.size()) return nullptr;
+  return g_trace.events[g_trace.used][which];
+}
+static void trace_mark(int which, cudaStream_t stream) {
+  cudaEvent_t ev = trace_event(which);
+  if (ev) cudaEventRecord(ev, stream);
+  if (ev && which == 2) ++g_trace.used;
+}
+
 static int fail(int code, const std::string& msg) {
   g_last_error = msg;
   return code;
@@ -782,6 +811,7 @@ int fcr_colreduce(const fcr_problem* problem, const void* q, const void* k, void
   if (e != cudaSuccess) return cuda_fail(e, "cudaMemsetAsync");
 
   // rows pass: Q stationary, K streamed
+  trace_mark(0, stream);
   PassParams pp;
   fill_common(pp, pr, pl, ws, false);
   rc = launch_pass_d<PH_ROWS, RED_SUM>(pl.d_pad, map_q, map_k, pp, pl.row_ctas, stream);
@@ -796,6 +826,7 @@ int fcr_colreduce(const fcr_problem* problem, const void* q, const void* k, void
   }
 
   // columns pass: K stationary, Q streamed
+  trace_mark(1, stream);
   fill_common(pp, pr, pl, ws, true);
   pp.out = out;
   pp.out_dtype = out_dtype;
@@ -813,6 +844,28 @@ int fcr_colreduce(const fcr_problem* problem, const void* q, const void* k, void
     e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "final_reduce launch");
   }
+  trace_mark(2, stream);
+  return FCR_OK;
+}
+
+int fcr_trace_enable(int32_t on) {
+  g_trace.on = on != 0;
+  g_trace.used = 0;
+  return FCR_OK;
+}
+
+int32_t fcr_trace_count(void) { return g_trace.used; }
+
+int fcr_trace_read(int32_t index, float* rows_ms, float* cols_ms) {
+  if (index < 0 || index >= g_trace.used || !rows_ms || !cols_ms)
+    return fail(FCR_ERR_BAD_ARG, "trace index out of range or null output");
+  auto& e = g_trace.events[index];
+  cudaError_t err = cudaEventSynchronize(e[2]);
+  if (err != cudaSuccess) return cuda_fail(err, "cudaEventSynchronize");
+  err = cudaEventElapsedTime(rows_ms, e[0], e[1]);
+  if (err != cudaSuccess) return cuda_fail(err, "cudaEventElapsedTime");
+  err = cudaEventElapsedTime(cols_ms, e[1], e[2]);
+  if (err != cudaSuccess) return cuda_fail(err, "cudaEventElapsedTime");
   return FCR_OK;
 }
 

@@ -164,6 +164,19 @@ int fcr_finalize(const float* acc, void* out, int32_t out_dtype, int32_t B, int3
 int fcr_read_device_status(const void* workspace, void* stream, int32_t* code_out);
 
 /*
+ * Tracing (the reference has none; its benchmark times whole calls on the
+ * host, benchmarks/run.py:59-83).  While enabled for the calling thread, each
+ * fcr_colreduce call records CUDA events on its stream before the rows pass,
+ * between the passes and after the last kernel (at most 256 calls are kept;
+ * enabling resets the count).  fcr_trace_read synchronises on call `index`
+ * and returns the device time of its rows pass (plus the split combine, if
+ * any) and of its columns pass (plus the final reduction, if any).
+ */
+int fcr_trace_enable(int32_t on);
+int32_t fcr_trace_count(void);
+int fcr_trace_read(int32_t index, float* rows_ms, float* cols_ms);
+
+/*
  * Bring-up diagnostic: writes the raw fp32 scores Q.K^T (no scale, no mask)
  * of every head into `scores`, a (B*H, m_pad, n_pad) fp32 device array, using
  * the same TMA / tcgen05 / tensor-memory pipeline as the operator.  Meant for
