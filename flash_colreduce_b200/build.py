@@ -49,6 +49,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
         return LIB_PATH
     os.makedirs(LIB_DIR, exist_ok=True)
     cmd = [_nvcc(), *NVCC_FLAGS]
+    cmd += os.environ.get("FCR_NVCC_EXTRA", "").split()  # tuning builds, e.g. -DFCR_CHUNK=32
     if verbose:
         cmd += ["-Xptxas", "-v"]
     cmd += ["-o", LIB_PATH] + [os.path.join(CSRC, s) for s in SOURCES]

@@ -46,9 +46,15 @@ enum { RED_SUM = 0, RED_MAX = 1 };
 
 constexpr int kSoftmaxWarps = 8;
 constexpr int kProducerWarp = 8;
-constexpr int kMmaWarp = 9;
-constexpr int kThreads = 320;
+constexpr int kMmaWarp = 9;                   // issues the MMAs of sub-tile 0, owns the TMEM allocation
+constexpr int kMmaWarp1 = 10;                 // issues the MMAs of sub-tile 1
+constexpr int kMmaWarps = 2;
+constexpr int kThreads = 352;
 constexpr int kTmemCols = 512;
+#ifndef FCR_CHUNK
+#define FCR_CHUNK 64
+#endif
+constexpr int kChunk = FCR_CHUNK;             // accumulator columns a softmax thread folds per step
 constexpr long long kWaitLimitCycles = 2000000000LL;  // about one second
 
 // Device status codes (status word 0).  Word 1: block, word 2: thread, word 3: detail.
@@ -86,8 +92,14 @@ struct SmemLayout {
   static constexpr int kTileBytes = kTile * DPAD * 2;
   static constexpr int kHalves = DPAD / 64;     // 64-element (128-byte) column slabs per tile
   static constexpr int kHalfBytes = kTile * 128;
-  static constexpr int KS = 2;                  // stationary stages (items in flight)
-  static constexpr int KR = (DPAD == 128) ? 3 : 6;  // streamed ring stages
+#ifndef FCR_KS
+#define FCR_KS 2
+#endif
+#ifndef FCR_KR
+#define FCR_KR 3
+#endif
+  static constexpr int KS = FCR_KS;             // stationary stages (items in flight)
+  static constexpr int KR = (DPAD == 128) ? FCR_KR : 2 * FCR_KR;  // streamed ring stages
   static constexpr int kLseBytes = kTile * 4;
   static constexpr int off_stat = 0;
   static constexpr int off_ring = off_stat + KS * kSubTiles * kTileBytes;
@@ -96,7 +108,7 @@ struct SmemLayout {
   static constexpr int kNumBars = 2 * KS + 2 * KR + 8;
   static constexpr int off_misc = off_bars + 8 * kNumBars;
   static constexpr int kBytes = off_misc + 16;
-  static constexpr int kDynamicBytes = kBytes + 1024;  // slack for manual 1024-byte alignment
+  static constexpr int kDynamicBytes = kBytes;
   static_assert(kDynamicBytes <= 232448, "exceeds the 227 KB shared memory of an sm_100 CTA");
 };
 
@@ -130,6 +142,28 @@ __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile
 }
 // Same, with a warp-uniform result so that .sync.aligned instructions that
 // follow are executed by all 32 lanes or by none.
+#ifdef FCR_PROFILE
+// Tuning builds only: cycles spent in each kind of wait, summed over lane 0 of
+// every warp, accumulated in shared memory and flushed to status words 16+.
+__shared__ unsigned long long g_prof[40];
+#endif
+#ifdef FCR_PROFILE
+#define PROF_T0() const long long prof_t = clock64()
+#define PROF_ADD(code) prof_acc[(code) % 10] += clock64() - prof_t
+#define PROF_DECL() long long prof_acc[10] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0}
+#define PROF_FLUSH(base)                                                              \
+  if ((threadIdx.x & 31) == 0) {                                                      \
+    _Pragma("unroll") for (int i_ = 0; i_ < 10; ++i_)                                 \
+        atomicAdd(&g_prof[(base) + i_], (unsigned long long)prof_acc[i_]);            \
+  }
+#define WAIT(bar, par, code) ([&]() { PROF_T0(); const bool ok_ = wait_bar_warp(bar, par, abort_flag, p.status, code); PROF_ADD(code); return ok_; }())
+#else
+#define PROF_T0()
+#define PROF_ADD(code)
+#define PROF_DECL()
+#define PROF_FLUSH(base)
+#define WAIT(bar, par, code) wait_bar_warp(bar, par, abort_flag, p.status, code)
+#endif
 __device__ __forceinline__ bool wait_bar_warp(uint32_t bar, uint32_t parity,
                                               volatile int* abort_flag, int* status, int code) {
   const bool ok = wait_bar(bar, parity, abort_flag, status, code);
@@ -155,18 +189,18 @@ __device__ __forceinline__ void store_out(void* out, int out_dtype, size_t idx, 
 // One 32-column chunk of a query row: online max / sum in the base-2 domain
 // (flash_colreduce/flash.py:71-78).  `nvalid` = number of leading columns of
 // the chunk this row may attend (only read when MASKED).
-template <bool MASKED>
-__device__ __forceinline__ void rows_chunk(const uint32_t (&r)[32], float scale2, int nvalid,
+template <bool MASKED, int W>
+__device__ __forceinline__ void rows_chunk(const uint32_t* r, float scale2, int nvalid,
                                            float& m_run, float& l_run) {
-  float x[32];
+  float x[W];
 #pragma unroll
-  for (int e = 0; e < 32; ++e) {
+  for (int e = 0; e < W; ++e) {
     x[e] = __uint_as_float(r[e]);
     if (MASKED && e >= nvalid) x[e] = -INFINITY;
   }
   float mx0 = fmaxf(x[0], x[1]), mx1 = fmaxf(x[2], x[3]);
 #pragma unroll
-  for (int e = 4; e < 32; e += 4) {
+  for (int e = 4; e < W; e += 4) {
     mx0 = fmaxf(mx0, fmaxf(x[e], x[e + 1]));
     mx1 = fmaxf(mx1, fmaxf(x[e + 2], x[e + 3]));
   }
@@ -176,7 +210,7 @@ __device__ __forceinline__ void rows_chunk(const uint32_t (&r)[32], float scale2
   const float nm = -m_safe;
   float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
 #pragma unroll
-  for (int e = 0; e < 32; e += 4) {
+  for (int e = 0; e < W; e += 4) {
     s0 += ptx::ex2(fmaf(x[e], scale2, nm));
     s1 += ptx::ex2(fmaf(x[e + 1], scale2, nm));
     s2 += ptx::ex2(fmaf(x[e + 2], scale2, nm));
@@ -191,11 +225,11 @@ __device__ __forceinline__ void rows_chunk(const uint32_t (&r)[32], float scale2
 // the column's accumulators (flash_colreduce/flash.py:120-124).  Queries
 // e in [e_lo, e_hi) of the chunk are valid (only read when MASKED).  For max
 // the fold is done on the exponent, exp2 being monotonic.
-template <int RED, bool MASKED>
-__device__ __forceinline__ void cols_chunk(const uint32_t (&r)[32], const float* neg_lse,
+template <int RED, bool MASKED, int W>
+__device__ __forceinline__ void cols_chunk(const uint32_t* r, const float* neg_lse,
                                            float scale2, int e_lo, int e_hi, float (&acc)[4]) {
 #pragma unroll
-  for (int q = 0; q < 8; ++q) {
+  for (int q = 0; q < W / 4; ++q) {
     const float4 nl = reinterpret_cast<const float4*>(neg_lse)[q];
     const float nlv[4] = {nl.x, nl.y, nl.z, nl.w};
 #pragma unroll
@@ -221,10 +255,14 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
             const __grid_constant__ CUtensorMap tmap_strm, const PassParams p) {
   using L = SmemLayout<DPAD>;
   constexpr int KS = L::KS, KR = L::KR;
-  extern __shared__ uint8_t smem_raw[];
-  const uint32_t raw_addr = ptx::smem_u32(smem_raw);
-  const uint32_t base = (raw_addr + 1023u) & ~1023u;
-  uint8_t* smem = smem_raw + (base - raw_addr);
+  // The 128-byte swizzle of the operand tiles needs a 1024-byte aligned base;
+  // the kernel uses no static shared memory, so the dynamic window starts there.
+  extern __shared__ __align__(1024) uint8_t smem[];
+  const uint32_t base = ptx::smem_u32(smem);
+  if ((base & 1023u) != 0) {
+    if (threadIdx.x == 0) report_status(p.status, ST_SMEM_MISALIGNED, (int)base);
+    return;
+  }
 
   const uint32_t s_stat = base + L::off_stat;
   const uint32_t s_ring = base + L::off_ring;
@@ -243,15 +281,19 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
 
   const int warp = (int)(threadIdx.x >> 5);
   const int lane = (int)(threadIdx.x & 31);
+#ifdef FCR_PROFILE
+  if (threadIdx.x < 40) g_prof[threadIdx.x] = 0;
+  const long long prof_t0 = clock64();
+#endif
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < KS; ++i) {
       ptx::mbar_init(bar_stat_full(i), 1);
-      ptx::mbar_init(bar_stat_empty(i), 1);
+      ptx::mbar_init(bar_stat_empty(i), kMmaWarps);
     }
     for (int i = 0; i < KR; ++i) {
       ptx::mbar_init(bar_ring_full(i), 1);
-      ptx::mbar_init(bar_ring_empty(i), PHASE == PH_COLS ? 1 + kSoftmaxWarps : 1);
+      ptx::mbar_init(bar_ring_empty(i), PHASE == PH_COLS ? kMmaWarps + kSoftmaxWarps : kMmaWarps);
     }
     for (int a = 0; a < 2; ++a)
       for (int ts = 0; ts < 2; ++ts) {
@@ -276,13 +318,14 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
 
   if (warp == kProducerWarp) {
     // ------------------------------------------------------------ TMA warp
+    PROF_DECL();
     uint32_t ring_seq = 0, item_seq = 0;
     bool ok = true;
     for (int item = (int)blockIdx.x; ok && item < p.n_items; item += (int)gridDim.x, ++item_seq) {
       const Item g = decode_item<PHASE == PH_COLS>(p, item);
       const int b = g.bh / p.H, h = g.bh - b * p.H;
       const uint32_t ks = item_seq % KS, kph = (item_seq / KS) & 1u;
-      ok = wait_bar_warp(bar_stat_empty(ks), kph ^ 1u, abort_flag, p.status, ST_WAIT_STAT_EMPTY);
+      ok = WAIT(bar_stat_empty(ks), kph ^ 1u, ST_WAIT_STAT_EMPTY);
       if (!ok) break;
       if (lane == 0) {
         ptx::mbar_arrive_expect_tx(bar_stat_full(ks), kSubTiles * L::kTileBytes);
@@ -296,8 +339,13 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
       __syncwarp();
       for (int t = g.c_lo; t < g.c_hi; ++t, ++ring_seq) {
         const uint32_t s = ring_seq % KR, ph = (ring_seq / KR) & 1u;
-        ok = wait_bar_warp(bar_ring_empty(s), ph ^ 1u, abort_flag, p.status, ST_WAIT_RING_EMPTY);
+        ok = WAIT(bar_ring_empty(s), ph ^ 1u, ST_WAIT_RING_EMPTY);
         if (!ok) break;
+#ifdef FCR_EXP_NOTMA
+        if (lane == 0 && ring_seq >= (uint32_t)KR) {
+          ptx::mbar_arrive(bar_ring_full(s));
+        } else
+#endif
         if (lane == 0) {
           ptx::mbar_arrive_expect_tx(bar_ring_full(s),
                                      L::kTileBytes + (PHASE == PH_COLS ? L::kLseBytes : 0));
@@ -313,49 +361,59 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
         __syncwarp();
       }
     }
-  } else if (warp == kMmaWarp) {
-    // ------------------------------------------------------------ MMA warp
-    uint32_t ring_seq = 0, item_seq = 0;
-    uint32_t tm_seq[kSubTiles] = {0, 0};
+#ifdef FCR_PROFILE
+    prof_acc[0] = clock64() - prof_t0;
+#endif
+    PROF_FLUSH(10);
+  } else if (warp == kMmaWarp || warp == kMmaWarp1) {
+    // ----------------------------------------------------------- MMA warps
+    // One issuing warp per stationary sub-tile: tcgen05.mma issue blocks while
+    // the tensor pipe's short queue is full, so with a single issuer the pipe
+    // drains during that warp's barrier handshakes; with two, one warp's
+    // handshakes overlap the other's MMAs.
+    PROF_DECL();
+    const int a = warp - kMmaWarp;
+    uint32_t ring_seq = 0, item_seq = 0, tm_seq = 0;
     bool ok = true;
     for (int item = (int)blockIdx.x; ok && item < p.n_items; item += (int)gridDim.x, ++item_seq) {
       const Item g = decode_item<PHASE == PH_COLS>(p, item);
       const uint32_t ks = item_seq % KS, kph = (item_seq / KS) & 1u;
-      ok = wait_bar_warp(bar_stat_full(ks), kph, abort_flag, p.status, ST_WAIT_STAT_FULL);
+      ok = WAIT(bar_stat_full(ks), kph, ST_WAIT_STAT_FULL);
       if (!ok) break;
       ptx::tc_fence_after_sync();
+      const uint32_t a_addr = s_stat + (ks * kSubTiles + a) * L::kTileBytes;
       for (int t = g.c_lo; ok && t < g.c_hi; ++t, ++ring_seq) {
         const uint32_t s = ring_seq % KR, ph = (ring_seq / KR) & 1u;
-        ok = wait_bar_warp(bar_ring_full(s), ph, abort_flag, p.status, ST_WAIT_RING_FULL);
-        if (!ok) break;
-        ptx::tc_fence_after_sync();
+        if (t >= g.t_lo[a] && t < g.t_hi[a]) {
+          ok = WAIT(bar_ring_full(s), ph, ST_WAIT_RING_FULL);
+          if (!ok) break;
+          const uint32_t ts = tm_seq & 1u, tph = (tm_seq >> 1) & 1u;
+          ok = WAIT(bar_tm_empty(a, ts), tph ^ 1u, ST_WAIT_TMEM_EMPTY);
+          if (!ok) break;
+          ptx::tc_fence_after_sync();
+          PROF_T0();
+          if (lane == 0) {
+            const uint32_t d = tmem_base + (uint32_t)(a * 2 + ts) * kTile;
+            const uint32_t b_addr = s_ring + s * L::kTileBytes;
 #pragma unroll
-        for (int a = 0; a < kSubTiles; ++a) {
-          if (ok && t >= g.t_lo[a] && t < g.t_hi[a]) {
-            const uint32_t ts = tm_seq[a] & 1u, tph = (tm_seq[a] >> 1) & 1u;
-            ok = wait_bar_warp(bar_tm_empty(a, ts), tph ^ 1u, abort_flag, p.status,
-                               ST_WAIT_TMEM_EMPTY);
-            if (ok) {
-              ptx::tc_fence_after_sync();
-              if (lane == 0) {
-                const uint32_t d = tmem_base + (uint32_t)(a * 2 + ts) * kTile;
-                const uint32_t a_addr = s_stat + (ks * kSubTiles + a) * L::kTileBytes;
-                const uint32_t b_addr = s_ring + s * L::kTileBytes;
-#pragma unroll
-                for (int kk = 0; kk < DPAD / 16; ++kk) {
-                  const uint32_t koff = (uint32_t)(kk >> 2) * L::kHalfBytes + (uint32_t)(kk & 3) * 32u;
-                  ptx::umma_f16(d, ptx::smem_desc_sw128(a_addr + koff),
-                                ptx::smem_desc_sw128(b_addr + koff), p.idesc, kk > 0 ? 1u : 0u);
-                }
-                ptx::umma_commit(bar_tm_full(a, ts));
-              }
-              __syncwarp();
-              ++tm_seq[a];
+            for (int kk = 0; kk < DPAD / 16; ++kk) {
+              const uint32_t koff = (uint32_t)(kk >> 2) * L::kHalfBytes + (uint32_t)(kk & 3) * 32u;
+              ptx::umma_f16(d, ptx::smem_desc_sw128(a_addr + koff),
+                            ptx::smem_desc_sw128(b_addr + koff), p.idesc, kk > 0 ? 1u : 0u);
             }
+            ptx::umma_commit(bar_tm_full(a, ts));
+            ptx::umma_commit(bar_ring_empty(s));
           }
+          __syncwarp();
+          PROF_ADD(25);
+          ++tm_seq;
+        } else {
+          // not this sub-tile's tile: release the slot once it has been filled
+          ok = WAIT(bar_ring_full(s), ph, ST_WAIT_RING_FULL);
+          if (!ok) break;
+          if (lane == 0) ptx::mbar_arrive(bar_ring_empty(s));
+          __syncwarp();
         }
-        if (ok && lane == 0) ptx::umma_commit(bar_ring_empty(s));
-        __syncwarp();
       }
       if (ok && lane == 0) ptx::umma_commit(bar_stat_empty(ks));
       __syncwarp();
@@ -364,11 +422,15 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
       // The last commit covers every MMA issued: wait for it so that no
       // asynchronous arrive is still outstanding when the CTA retires.
       const uint32_t last = item_seq - 1;
-      wait_bar_warp(bar_stat_empty(last % KS), (last / KS) & 1u, abort_flag, p.status,
-                    ST_WAIT_DRAIN);
+      WAIT(bar_stat_empty(last % KS), (last / KS) & 1u, ST_WAIT_DRAIN);
     }
+#ifdef FCR_PROFILE
+    prof_acc[0] = clock64() - prof_t0;
+#endif
+    PROF_FLUSH(20);
   } else {
     // -------------------------------------------------------- softmax warps
+    PROF_DECL();
     const int a = warp >> 2;
     const int tid_wg = (warp & 3) * 32 + lane;
     const uint32_t lane_field = (uint32_t)((warp & 3) * 32) << 16;
@@ -387,12 +449,12 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
         const uint32_t rs = ring_base + (uint32_t)(t - g.c_lo);
         const uint32_t s = rs % KR, rph = (rs / KR) & 1u;
         if (PHASE == PH_COLS) {
-          ok = wait_bar_warp(bar_ring_full(s), rph, abort_flag, p.status, ST_WAIT_RING_FULL_SM);
+          ok = WAIT(bar_ring_full(s), rph, ST_WAIT_RING_FULL_SM);
           if (!ok) break;
         }
         if (active) {
           const uint32_t ts = tm_seq & 1u, tph = (tm_seq >> 1) & 1u;
-          ok = wait_bar_warp(bar_tm_full(a, ts), tph, abort_flag, p.status, ST_WAIT_TMEM_FULL);
+          ok = WAIT(bar_tm_full(a, ts), tph, ST_WAIT_TMEM_FULL);
           if (!ok) break;
           ptx::tc_fence_after_sync();
           const uint32_t taddr = tmem_base + lane_field + (uint32_t)(a * 2 + ts) * kTile;
@@ -414,46 +476,69 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
           if (PHASE == PH_DUMP) need_mask = false;
           const float* lse_s = reinterpret_cast<const float*>(smem + L::off_lse + s * L::kLseBytes);
 
-          uint32_t ra[32], rb[32];
-          auto consume = [&](const uint32_t (&r)[32], int c) {
+          uint32_t ra[kChunk], rb[kChunk];
+          auto consume = [&](const uint32_t* r, int c) {
             if constexpr (PHASE == PH_DUMP) {
               if (mine < p.m_pad) {
                 float4* dst = reinterpret_cast<float4*>(
-                    p.dump + ((size_t)g.bh * p.m_pad + mine) * p.n_pad + c0 + 32 * c);
+                    p.dump + ((size_t)g.bh * p.m_pad + mine) * p.n_pad + c0 + kChunk * c);
 #pragma unroll
-                for (int q = 0; q < 8; ++q)
+                for (int q = 0; q < kChunk / 4; ++q)
                   dst[q] = make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
                                        __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
               }
             } else if constexpr (PHASE == PH_ROWS) {
               if (need_mask)
-                rows_chunk<true>(r, p.scale2, lim_hi - 32 * c, m_run, l_run);
+                rows_chunk<true, kChunk>(r, p.scale2, lim_hi - kChunk * c, m_run, l_run);
               else
-                rows_chunk<false>(r, p.scale2, 32, m_run, l_run);
+                rows_chunk<false, kChunk>(r, p.scale2, kChunk, m_run, l_run);
             } else {
               if (need_mask)
-                cols_chunk<RED, true>(r, lse_s + 32 * c, p.scale2, lim_lo - 32 * c,
-                                      lim_hi - 32 * c, acc);
+                cols_chunk<RED, true, kChunk>(r, lse_s + kChunk * c, p.scale2, lim_lo - kChunk * c,
+                                              lim_hi - kChunk * c, acc);
               else
-                cols_chunk<RED, false>(r, lse_s + 32 * c, p.scale2, 0, 32, acc);
+                cols_chunk<RED, false, kChunk>(r, lse_s + kChunk * c, p.scale2, 0, kChunk, acc);
             }
           };
-          ptx::tmem_ld32(taddr, ra);
-          ptx::tmem_ld_wait(ra);
-          ptx::tmem_ld32(taddr + 32, rb);
-          consume(ra, 0);
-          ptx::tmem_ld_wait(rb);
-          ptx::tmem_ld32(taddr + 64, ra);
-          consume(rb, 1);
-          ptx::tmem_ld_wait(ra);
-          ptx::tmem_ld32(taddr + 96, rb);
-          consume(ra, 2);
-          ptx::tmem_ld_wait(rb);
-          // every lane has its copy of the tile: hand the accumulator back
-          ptx::tc_fence_before_sync();
-          __syncwarp();
-          if (lane == 0) ptx::mbar_arrive(bar_tm_empty(a, ts));
-          consume(rb, 3);
+#ifdef FCR_EXP_NOSOFTMAX
+          if (true) {
+            ptx::tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(bar_tm_empty(a, ts));
+            acc[0] += 1.f;
+            l_run += 1.f;
+          } else
+#endif
+          // chunk c+1 is in flight from tensor memory while chunk c is folded
+          {
+            PROF_T0();
+            ptx::tmem_ld<kChunk>(taddr, ra);
+            ptx::tmem_ld_wait<kChunk>(ra);
+            PROF_ADD(33);
+#pragma unroll
+          for (int c = 0; c < kTile / kChunk; ++c) {
+            uint32_t* cur = (c & 1) ? rb : ra;
+            uint32_t* nxt = (c & 1) ? ra : rb;
+            if (c + 1 < kTile / kChunk) {
+              ptx::tmem_ld<kChunk>(taddr + (c + 1) * kChunk, nxt);
+            } else {
+              // every lane holds the rest of the tile: hand the accumulator back
+              ptx::tc_fence_before_sync();
+              __syncwarp();
+              if (lane == 0) ptx::mbar_arrive(bar_tm_empty(a, ts));
+            }
+            {
+              PROF_T0();
+              consume(cur, c);
+              PROF_ADD(34);
+            }
+            if (c + 1 < kTile / kChunk) {
+              PROF_T0();
+              ptx::tmem_ld_wait<kChunk>(nxt);
+              PROF_ADD(35);
+            }
+          }
+          }
           ++tm_seq;
         }
         if (PHASE == PH_COLS) {
@@ -491,6 +576,10 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
         }
       }
     }
+#ifdef FCR_PROFILE
+    prof_acc[0] = clock64() - prof_t0;
+#endif
+    PROF_FLUSH(30);
   }
 
   // ------------------------------------------------------------- teardown
@@ -507,6 +596,11 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
     ptx::tc_fence_after_sync();
     ptx::tmem_dealloc(tmem_base, kTmemCols);
   }
+#ifdef FCR_PROFILE
+  if (threadIdx.x < 40)
+    atomicAdd(reinterpret_cast<unsigned long long*>(p.status + 16) + threadIdx.x +
+                  (PHASE == PH_COLS ? 40 : 0), g_prof[threadIdx.x]);
+#endif
 }
 
 // Combines the per-split running (max, sum) of the rows pass into -lse.

@@ -21,7 +21,7 @@ namespace fcr {
 constexpr int kTile = 128;            // rows per MMA tile (tensor-memory lanes)
 constexpr int kSubTiles = 2;          // stationary tiles a CTA owns
 constexpr int kBlockRows = kTile * kSubTiles;
-constexpr int kStatusWords = 64;
+constexpr int kStatusWords = 256;
 
 // Geometry of one pass, shared by the host planner and the kernels.
 struct PassGeom {

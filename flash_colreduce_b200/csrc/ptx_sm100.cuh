@@ -106,8 +106,8 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
                : "memory");
 }
 // 32 lanes x 32 consecutive fp32 columns: thread l of the warp receives lane
-// (base_lane + l), columns [col, col+32).
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+// (base_lane + l), columns [col, col+32), in r[0..31].
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
       "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -120,10 +120,10 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
       : "r"(taddr)
       : "memory");
 }
-// Waits for this thread's outstanding tcgen05.ld.  The registers are threaded
-// through the statement so that no use of them can be scheduled above it.
-__device__ __forceinline__ void tmem_ld_wait(uint32_t (&r)[32]) {
-  asm volatile("tcgen05.wait::ld.sync.aligned;"
+// Threads 32 registers through an (empty) statement so that no use of them can
+// be scheduled above the wait that precedes it.
+__device__ __forceinline__ void pin32(uint32_t* r) {
+  asm volatile(""
                : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]),
                  "+r"(r[6]), "+r"(r[7]), "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]),
                  "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]), "+r"(r[16]), "+r"(r[17]),
@@ -132,6 +132,19 @@ __device__ __forceinline__ void tmem_ld_wait(uint32_t (&r)[32]) {
                  "+r"(r[30]), "+r"(r[31])
                :
                : "memory");
+}
+// W (a multiple of 32) consecutive columns into r[0..W).
+template <int W>
+__device__ __forceinline__ void tmem_ld(uint32_t taddr, uint32_t* r) {
+#pragma unroll
+  for (int i = 0; i < W / 32; ++i) tmem_ld32(taddr + 32 * i, r + 32 * i);
+}
+// Waits for this thread's outstanding tcgen05.ld; r[0..W) are usable afterwards.
+template <int W>
+__device__ __forceinline__ void tmem_ld_wait(uint32_t* r) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < W / 32; ++i) pin32(r + 32 * i);
 }
 
 // ---------------------------------------------------------------------- math

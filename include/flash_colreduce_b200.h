@@ -89,7 +89,7 @@ typedef struct fcr_plan {
   int64_t causal_offset;    /* resolved offset */
   int64_t valid_scores;     /* B*H*sum_i valid(i): the unit the throughput metric counts */
   /* workspace layout, byte offsets from the workspace base */
-  int64_t off_status;       /* int32[64] device status words */
+  int64_t off_status;       /* int32[256] device status words (word 0: first failure code) */
   int64_t off_neg_lse;      /* float[B*H][m_pad]: minus the base-2 log-sum-exp of each query row */
   int64_t off_part_m;       /* float[row_splits][B*H][m_pad] running maxima (row_splits > 1) */
   int64_t off_part_l;       /* float[row_splits][B*H][m_pad] running sums   (row_splits > 1) */
