@@ -30,6 +30,7 @@
 #include <cuda_runtime.h>
 #include <math.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <array>
@@ -44,17 +45,26 @@ namespace fcr {
 enum { PH_DUMP = 0, PH_ROWS = 1, PH_COLS = 2 };
 enum { RED_SUM = 0, RED_MAX = 1 };
 
-constexpr int kSoftmaxWarps = 8;
-constexpr int kProducerWarp = 8;
-constexpr int kMmaWarp = 9;                   // issues the MMAs of sub-tile 0, owns the TMEM allocation
-constexpr int kMmaWarp1 = 10;                 // issues the MMAs of sub-tile 1
-constexpr int kMmaWarps = 2;
-constexpr int kThreads = 352;
-constexpr int kTmemCols = 512;
-#ifndef FCR_CHUNK
-#define FCR_CHUNK 64
+#ifndef FCR_COLSPLIT
+#define FCR_COLSPLIT 2
 #endif
-constexpr int kChunk = FCR_CHUNK;             // accumulator columns a softmax thread folds per step
+constexpr int kColSplit = FCR_COLSPLIT;       // softmax warpgroups sharing one accumulator tile
+constexpr int kSoftmaxWarps = 4 * kSubTiles * kColSplit;
+constexpr int kProducerWarp = kSoftmaxWarps;
+constexpr int kMmaWarp = kSoftmaxWarps + 1;   // issues the MMAs of sub-tile 0, owns the TMEM allocation
+constexpr int kMmaWarps = kSubTiles;          // one issuing warp per stationary sub-tile
+constexpr int kThreads = (kSoftmaxWarps + 1 + kMmaWarps) * 32;
+constexpr int kTmemCols = 512;
+constexpr int kSpan = kTile / kColSplit;      // accumulator columns of a tile one softmax thread folds
+#ifndef FCR_CHUNK
+#define FCR_CHUNK 32
+#endif
+constexpr int kChunk = FCR_CHUNK;             // columns per tensor-memory load
+#ifndef FCR_POLY
+#define FCR_POLY 2
+#endif
+constexpr int kPolyOf8 = FCR_POLY;            // exponentials per 8 taken off the MUFU pipe (0, 2, 4, 6)
+static_assert(kSpan % kChunk == 0 && kChunk % 32 == 0, "chunk must divide the per-thread span");
 constexpr long long kWaitLimitCycles = 2000000000LL;  // about one second
 
 // Device status codes (status word 0).  Word 1: block, word 2: thread, word 3: detail.
@@ -69,6 +79,11 @@ enum {
   ST_WAIT_DRAIN = 24,
   ST_WAIT_TMEM_FULL = 31,
   ST_WAIT_RING_FULL_SM = 32,
+  ST_WAIT_SCHED_EMPTY = 13,
+  ST_WAIT_SCHED_FULL = 26,
+  ST_WAIT_SCHED_FULL_SM = 38,
+  ST_WAIT_MERGE_FULL = 36,
+  ST_WAIT_MERGE_EMPTY = 37,
 };
 
 struct PassParams : PassGeom {
@@ -85,6 +100,7 @@ struct PassParams : PassGeom {
   int mean_mode;   // 0: none, 1: divide by div_M, 2: causal rule
   int div_M, div_N, div_c;
   int* status;
+  int* sched_counter;  // zero at launch; hands out work items beyond the first gridDim.x
 };
 
 template <int DPAD>
@@ -93,10 +109,10 @@ struct SmemLayout {
   static constexpr int kHalves = DPAD / 64;     // 64-element (128-byte) column slabs per tile
   static constexpr int kHalfBytes = kTile * 128;
 #ifndef FCR_KS
-#define FCR_KS 2
+#define FCR_KS 1
 #endif
 #ifndef FCR_KR
-#define FCR_KR 3
+#define FCR_KR 4
 #endif
   static constexpr int KS = FCR_KS;             // stationary stages (items in flight)
   static constexpr int KR = (DPAD == 128) ? FCR_KR : 2 * FCR_KR;  // streamed ring stages
@@ -104,10 +120,13 @@ struct SmemLayout {
   static constexpr int off_stat = 0;
   static constexpr int off_ring = off_stat + KS * kSubTiles * kTileBytes;
   static constexpr int off_lse = off_ring + KR * kTileBytes;
-  static constexpr int off_bars = off_lse + KR * kLseBytes;
-  static constexpr int kNumBars = 2 * KS + 2 * KR + 8;
+  static constexpr int off_merge = off_lse + KR * kLseBytes;  // float2 [2 slots][kSubTiles][kTile]
+  static constexpr int kMergeBytes = (kColSplit > 1) ? 2 * kSubTiles * kTile * 8 : 0;
+  static constexpr int off_bars = off_merge + kMergeBytes;
+  static constexpr int KI = 4;                   // work items announced ahead of their consumers
+  static constexpr int kNumBars = 2 * KS + 2 * KR + 8 + 8 + 2 * KI;
   static constexpr int off_misc = off_bars + 8 * kNumBars;
-  static constexpr int kBytes = off_misc + 16;
+  static constexpr int kBytes = off_misc + 16 + 4 * KI;
   static constexpr int kDynamicBytes = kBytes;
   static_assert(kDynamicBytes <= 232448, "exceeds the 227 KB shared memory of an sm_100 CTA");
 };
@@ -198,25 +217,42 @@ __device__ __forceinline__ void rows_chunk(const uint32_t* r, float scale2, int 
     x[e] = __uint_as_float(r[e]);
     if (MASKED && e >= nvalid) x[e] = -INFINITY;
   }
-  float mx0 = fmaxf(x[0], x[1]), mx1 = fmaxf(x[2], x[3]);
+  float mx0 = ptx::max3(x[0], x[1], x[2]), mx1 = ptx::max3(x[3], x[4], x[5]);
+  mx0 = fmaxf(mx0, x[6]);
+  mx1 = fmaxf(mx1, x[7]);
 #pragma unroll
-  for (int e = 4; e < W; e += 4) {
-    mx0 = fmaxf(mx0, fmaxf(x[e], x[e + 1]));
-    mx1 = fmaxf(mx1, fmaxf(x[e + 2], x[e + 3]));
+  for (int e = 8; e < W; e += 4) {
+    mx0 = ptx::max3(mx0, x[e], x[e + 1]);
+    mx1 = ptx::max3(mx1, x[e + 2], x[e + 3]);
   }
   const float m_new = fmaxf(m_run, fmaxf(mx0, mx1) * scale2);
   const float m_safe = (m_new == -INFINITY) ? 0.f : m_new;  // row sees nothing yet
   const float alpha = ptx::ex2(m_run - m_safe);
   const float nm = -m_safe;
-  float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+  float2 s01 = make_float2(0.f, 0.f), s23 = make_float2(0.f, 0.f);
 #pragma unroll
   for (int e = 0; e < W; e += 4) {
-    s0 += ptx::ex2(fmaf(x[e], scale2, nm));
-    s1 += ptx::ex2(fmaf(x[e + 1], scale2, nm));
-    s2 += ptx::ex2(fmaf(x[e + 2], scale2, nm));
-    s3 += ptx::ex2(fmaf(x[e + 3], scale2, nm));
+    float2 a01 = __ffma2_rn(make_float2(x[e], x[e + 1]), make_float2(scale2, scale2),
+                            make_float2(nm, nm));
+    float2 a23 = __ffma2_rn(make_float2(x[e + 2], x[e + 3]), make_float2(scale2, scale2),
+                            make_float2(nm, nm));
+    // kPolyOf8 of every 8 exponentials are evaluated on the FMA pipe (never in masked tiles)
+    if (!MASKED && (e & 7) < kPolyOf8) {
+      a01 = ptx::ex2_poly2(a01);
+    } else {
+      a01.x = ptx::ex2(a01.x);
+      a01.y = ptx::ex2(a01.y);
+    }
+    if (!MASKED && ((e + 2) & 7) < kPolyOf8) {
+      a23 = ptx::ex2_poly2(a23);
+    } else {
+      a23.x = ptx::ex2(a23.x);
+      a23.y = ptx::ex2(a23.y);
+    }
+    s01 = __fadd2_rn(s01, a01);
+    s23 = __fadd2_rn(s23, a23);
   }
-  l_run = fmaf(l_run, alpha, (s0 + s1) + (s2 + s3));
+  l_run = fmaf(l_run, alpha, (s01.x + s01.y) + (s23.x + s23.y));
   m_run = m_new;
 }
 
@@ -231,20 +267,44 @@ __device__ __forceinline__ void cols_chunk(const uint32_t* r, const float* neg_l
 #pragma unroll
   for (int q = 0; q < W / 4; ++q) {
     const float4 nl = reinterpret_cast<const float4*>(neg_lse)[q];
-    const float nlv[4] = {nl.x, nl.y, nl.z, nl.w};
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const int e = q * 4 + u;
-      float t = fmaf(__uint_as_float(r[e]), scale2, nlv[u]);
-      const bool valid = !MASKED || (e >= e_lo && e < e_hi);
-      if (RED == RED_SUM) {
-        float pr = ptx::ex2(t);
-        if (MASKED) pr = valid ? pr : 0.f;
-        acc[u] += pr;
+    const int e = q * 4;
+    float2 t01 = __ffma2_rn(make_float2(__uint_as_float(r[e]), __uint_as_float(r[e + 1])),
+                            make_float2(scale2, scale2), make_float2(nl.x, nl.y));
+    float2 t23 = __ffma2_rn(make_float2(__uint_as_float(r[e + 2]), __uint_as_float(r[e + 3])),
+                            make_float2(scale2, scale2), make_float2(nl.z, nl.w));
+    if (RED == RED_SUM) {
+      // kPolyOf8 of every 8 exponentials are evaluated on the FMA pipe (never in masked tiles)
+      if (!MASKED && (e & 7) < kPolyOf8) {
+        t01 = ptx::ex2_poly2(t01);
       } else {
-        if (MASKED) t = valid ? t : -INFINITY;
-        acc[u] = fmaxf(acc[u], t);
+        t01.x = ptx::ex2(t01.x);
+        t01.y = ptx::ex2(t01.y);
       }
+      if (!MASKED && ((e + 2) & 7) < kPolyOf8) {
+        t23 = ptx::ex2_poly2(t23);
+      } else {
+        t23.x = ptx::ex2(t23.x);
+        t23.y = ptx::ex2(t23.y);
+      }
+      if (MASKED) {
+        t01.x = (e >= e_lo && e < e_hi) ? t01.x : 0.f;
+        t01.y = (e + 1 >= e_lo && e + 1 < e_hi) ? t01.y : 0.f;
+        t23.x = (e + 2 >= e_lo && e + 2 < e_hi) ? t23.x : 0.f;
+        t23.y = (e + 3 >= e_lo && e + 3 < e_hi) ? t23.y : 0.f;
+      }
+      acc[0] += t01.x;
+      acc[1] += t01.y;
+      acc[2] += t23.x;
+      acc[3] += t23.y;
+    } else {
+      if (MASKED) {
+        t01.x = (e >= e_lo && e < e_hi) ? t01.x : -INFINITY;
+        t01.y = (e + 1 >= e_lo && e + 1 < e_hi) ? t01.y : -INFINITY;
+        t23.x = (e + 2 >= e_lo && e + 2 < e_hi) ? t23.x : -INFINITY;
+        t23.y = (e + 3 >= e_lo && e + 3 < e_hi) ? t23.y : -INFINITY;
+      }
+      acc[0] = ptx::max3(acc[0], t01.x, t01.y);
+      acc[1] = ptx::max3(acc[1], t23.x, t23.y);
     }
   }
 }
@@ -276,8 +336,18 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
   auto bar_tm_empty = [&](uint32_t a, uint32_t ts) {
     return bar0 + 8u * (2 * KS + 2 * KR + 4 + a * 2 + ts);
   };
+  auto bar_merge_full = [&](uint32_t a, uint32_t slot) {
+    return bar0 + 8u * (2 * KS + 2 * KR + 8 + a * 2 + slot);
+  };
+  auto bar_merge_empty = [&](uint32_t a, uint32_t slot) {
+    return bar0 + 8u * (2 * KS + 2 * KR + 12 + a * 2 + slot);
+  };
+  constexpr int KI = L::KI;
+  auto bar_sched_full = [&](uint32_t i) { return bar0 + 8u * (2 * KS + 2 * KR + 16 + i); };
+  auto bar_sched_empty = [&](uint32_t i) { return bar0 + 8u * (2 * KS + 2 * KR + 16 + KI + i); };
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + L::off_misc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::off_misc + 4);
+  volatile int* sched_item = reinterpret_cast<volatile int*>(smem + L::off_misc + 16);
 
   const int warp = (int)(threadIdx.x >> 5);
   const int lane = (int)(threadIdx.x & 31);
@@ -298,8 +368,14 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
     for (int a = 0; a < 2; ++a)
       for (int ts = 0; ts < 2; ++ts) {
         ptx::mbar_init(bar_tm_full(a, ts), 1);
-        ptx::mbar_init(bar_tm_empty(a, ts), 4);
+        ptx::mbar_init(bar_tm_empty(a, ts), 4 * kColSplit);
+        ptx::mbar_init(bar_merge_full(a, ts), kColSplit > 1 ? 4 * (kColSplit - 1) : 1);
+        ptx::mbar_init(bar_merge_empty(a, ts), 4);
       }
+    for (int i = 0; i < KI; ++i) {
+      ptx::mbar_init(bar_sched_full(i), 1);
+      ptx::mbar_init(bar_sched_empty(i), kMmaWarps + kSoftmaxWarps);
+    }
     *abort_flag = 0;
     ptx::fence_mbar_init();
   }
@@ -319,9 +395,25 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
   if (warp == kProducerWarp) {
     // ------------------------------------------------------------ TMA warp
     PROF_DECL();
+    // Work items are handed out dynamically: the first is the CTA's own index,
+    // later ones come from a global counter.  Each is announced to the other
+    // warps through a small ring in shared memory; -1 ends the kernel.
     uint32_t ring_seq = 0, item_seq = 0;
     bool ok = true;
-    for (int item = (int)blockIdx.x; ok && item < p.n_items; item += (int)gridDim.x, ++item_seq) {
+    int item = (int)blockIdx.x;
+    for (;; ++item_seq) {
+      const uint32_t si = item_seq % KI, sph = (item_seq / KI) & 1u;
+      ok = WAIT(bar_sched_empty(si), sph ^ 1u, ST_WAIT_SCHED_EMPTY);
+      if (!ok) break;
+      const bool last = item >= p.n_items;
+      int next_item = 0;
+      if (lane == 0) {
+        sched_item[si] = last ? -1 : item;
+        ptx::mbar_arrive(bar_sched_full(si));
+        if (!last) next_item = (int)gridDim.x + atomicAdd(p.sched_counter, 1);
+      }
+      __syncwarp();
+      if (last) break;
       const Item g = decode_item<PHASE == PH_COLS>(p, item);
       const int b = g.bh / p.H, h = g.bh - b * p.H;
       const uint32_t ks = item_seq % KS, kph = (item_seq / KS) & 1u;
@@ -341,11 +433,6 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
         const uint32_t s = ring_seq % KR, ph = (ring_seq / KR) & 1u;
         ok = WAIT(bar_ring_empty(s), ph ^ 1u, ST_WAIT_RING_EMPTY);
         if (!ok) break;
-#ifdef FCR_EXP_NOTMA
-        if (lane == 0 && ring_seq >= (uint32_t)KR) {
-          ptx::mbar_arrive(bar_ring_full(s));
-        } else
-#endif
         if (lane == 0) {
           ptx::mbar_arrive_expect_tx(bar_ring_full(s),
                                      L::kTileBytes + (PHASE == PH_COLS ? L::kLseBytes : 0));
@@ -360,12 +447,14 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
         }
         __syncwarp();
       }
+      if (!ok) break;
+      item = __shfl_sync(0xffffffffu, next_item, 0);
     }
 #ifdef FCR_PROFILE
     prof_acc[0] = clock64() - prof_t0;
 #endif
     PROF_FLUSH(10);
-  } else if (warp == kMmaWarp || warp == kMmaWarp1) {
+  } else if (warp >= kMmaWarp) {
     // ----------------------------------------------------------- MMA warps
     // One issuing warp per stationary sub-tile: tcgen05.mma issue blocks while
     // the tensor pipe's short queue is full, so with a single issuer the pipe
@@ -375,7 +464,14 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
     const int a = warp - kMmaWarp;
     uint32_t ring_seq = 0, item_seq = 0, tm_seq = 0;
     bool ok = true;
-    for (int item = (int)blockIdx.x; ok && item < p.n_items; item += (int)gridDim.x, ++item_seq) {
+    for (;; ++item_seq) {
+      const uint32_t si = item_seq % KI, sph = (item_seq / KI) & 1u;
+      ok = WAIT(bar_sched_full(si), sph, ST_WAIT_SCHED_FULL);
+      if (!ok) break;
+      const int item = sched_item[si];
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(bar_sched_empty(si));
+      if (item < 0) break;
       const Item g = decode_item<PHASE == PH_COLS>(p, item);
       const uint32_t ks = item_seq % KS, kph = (item_seq / KS) & 1u;
       ok = WAIT(bar_stat_full(ks), kph, ST_WAIT_STAT_FULL);
@@ -384,9 +480,9 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
       const uint32_t a_addr = s_stat + (ks * kSubTiles + a) * L::kTileBytes;
       for (int t = g.c_lo; ok && t < g.c_hi; ++t, ++ring_seq) {
         const uint32_t s = ring_seq % KR, ph = (ring_seq / KR) & 1u;
+        ok = WAIT(bar_ring_full(s), ph, ST_WAIT_RING_FULL);
+        if (!ok) break;
         if (t >= g.t_lo[a] && t < g.t_hi[a]) {
-          ok = WAIT(bar_ring_full(s), ph, ST_WAIT_RING_FULL);
-          if (!ok) break;
           const uint32_t ts = tm_seq & 1u, tph = (tm_seq >> 1) & 1u;
           ok = WAIT(bar_tm_empty(a, ts), tph ^ 1u, ST_WAIT_TMEM_EMPTY);
           if (!ok) break;
@@ -408,14 +504,13 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
           PROF_ADD(25);
           ++tm_seq;
         } else {
-          // not this sub-tile's tile: release the slot once it has been filled
-          ok = WAIT(bar_ring_full(s), ph, ST_WAIT_RING_FULL);
-          if (!ok) break;
+          // not this sub-tile's tile: the slot is released as soon as it has been filled
           if (lane == 0) ptx::mbar_arrive(bar_ring_empty(s));
           __syncwarp();
         }
       }
-      if (ok && lane == 0) ptx::umma_commit(bar_stat_empty(ks));
+      if (!ok) break;
+      if (lane == 0) ptx::umma_commit(bar_stat_empty(ks));
       __syncwarp();
     }
     if (ok && item_seq > 0) {
@@ -430,13 +525,26 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
     PROF_FLUSH(20);
   } else {
     // -------------------------------------------------------- softmax warps
+    // Warp w reads tensor-memory lanes 32*(w%4).. (a hardware rule), belongs to
+    // stationary sub-tile a and folds columns [part*kSpan, (part+1)*kSpan) of
+    // each of that sub-tile's accumulator tiles.
     PROF_DECL();
-    const int a = warp >> 2;
+    const int a = (warp >> 2) % kSubTiles;
+    const int part = warp / (4 * kSubTiles);
     const int tid_wg = (warp & 3) * 32 + lane;
     const uint32_t lane_field = (uint32_t)((warp & 3) * 32) << 16;
-    uint32_t ring_base = 0, tm_seq = 0;
+    const int col_base = part * kSpan;  // first accumulator column this thread folds
+    float2* merge_buf = reinterpret_cast<float2*>(smem + L::off_merge);
+    uint32_t ring_base = 0, tm_seq = 0, merge_seq = 0;
     bool ok = true;
-    for (int item = (int)blockIdx.x; ok && item < p.n_items; item += (int)gridDim.x) {
+    for (uint32_t item_seq = 0;; ++item_seq) {
+      const uint32_t si = item_seq % KI, sph = (item_seq / KI) & 1u;
+      ok = WAIT(bar_sched_full(si), sph, ST_WAIT_SCHED_FULL_SM);
+      if (!ok) break;
+      const int item = sched_item[si];
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(bar_sched_empty(si));
+      if (item < 0) break;
       const Item g = decode_item<PHASE == PH_COLS>(p, item);
       const int mine = g.r0[a] + tid_wg;  // query row (rows pass) or key column (columns pass)
       float m_run = -INFINITY, l_run = 0.f;
@@ -457,36 +565,38 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
           ok = WAIT(bar_tm_full(a, ts), tph, ST_WAIT_TMEM_FULL);
           if (!ok) break;
           ptx::tc_fence_after_sync();
-          const uint32_t taddr = tmem_base + lane_field + (uint32_t)(a * 2 + ts) * kTile;
-          const int c0 = t * kTile;  // first streamed index of the tile
+          const uint32_t taddr =
+              tmem_base + lane_field + (uint32_t)(a * 2 + ts) * kTile + (uint32_t)col_base;
+          const int c0 = t * kTile + col_base;  // streamed index of this thread's first column
           bool need_mask;
           int lim_lo = 0, lim_hi = 0;
           if (PHASE == PH_COLS) {
             // valid queries i: max(mine - off, 0) <= i < M
-            need_mask = (c0 + kTile > p.M) || (p.causal && (c0 + p.off < g.r0[a] + kTile - 1));
+            need_mask = (t * kTile + kTile > p.M) ||
+                        (p.causal && (t * kTile + p.off < g.r0[a] + kTile - 1));
             lim_lo = p.causal ? max(mine - p.off, 0) - c0 : -(1 << 30);
             lim_hi = p.M - c0;
           } else {
             // valid keys j: j <= min(N - 1, mine + off)
-            need_mask = (c0 + kTile > p.N) || (p.causal && (c0 + kTile - 1 > g.r0[a] + p.off));
+            need_mask = (t * kTile + kTile > p.N) ||
+                        (p.causal && (t * kTile + kTile - 1 > g.r0[a] + p.off));
             const long long jlim =
                 p.causal ? min((long long)p.N - 1, (long long)mine + p.off) : (long long)p.N - 1;
-            lim_hi = (int)(jlim - c0 + 1);
+            lim_hi = (int)max(min(jlim - c0 + 1, (long long)(1 << 20)), (long long)-(1 << 20));
           }
           if (PHASE == PH_DUMP) need_mask = false;
-          const float* lse_s = reinterpret_cast<const float*>(smem + L::off_lse + s * L::kLseBytes);
+          const float* lse_s =
+              reinterpret_cast<const float*>(smem + L::off_lse + s * L::kLseBytes) + col_base;
 
           uint32_t ra[kChunk], rb[kChunk];
           auto consume = [&](const uint32_t* r, int c) {
             if constexpr (PHASE == PH_DUMP) {
-              if (mine < p.m_pad) {
-                float4* dst = reinterpret_cast<float4*>(
-                    p.dump + ((size_t)g.bh * p.m_pad + mine) * p.n_pad + c0 + kChunk * c);
+              float4* dst = reinterpret_cast<float4*>(
+                  p.dump + ((size_t)g.bh * p.m_pad + mine) * p.n_pad + c0 + kChunk * c);
 #pragma unroll
-                for (int q = 0; q < kChunk / 4; ++q)
-                  dst[q] = make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
-                                       __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
-              }
+              for (int q = 0; q < kChunk / 4; ++q)
+                dst[q] = make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
+                                     __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
             } else if constexpr (PHASE == PH_ROWS) {
               if (need_mask)
                 rows_chunk<true, kChunk>(r, p.scale2, lim_hi - kChunk * c, m_run, l_run);
@@ -500,29 +610,21 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
                 cols_chunk<RED, false, kChunk>(r, lse_s + kChunk * c, p.scale2, 0, kChunk, acc);
             }
           };
-#ifdef FCR_EXP_NOSOFTMAX
-          if (true) {
-            ptx::tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(bar_tm_empty(a, ts));
-            acc[0] += 1.f;
-            l_run += 1.f;
-          } else
-#endif
           // chunk c+1 is in flight from tensor memory while chunk c is folded
           {
             PROF_T0();
             ptx::tmem_ld<kChunk>(taddr, ra);
             ptx::tmem_ld_wait<kChunk>(ra);
             PROF_ADD(33);
+          }
 #pragma unroll
-          for (int c = 0; c < kTile / kChunk; ++c) {
+          for (int c = 0; c < kSpan / kChunk; ++c) {
             uint32_t* cur = (c & 1) ? rb : ra;
             uint32_t* nxt = (c & 1) ? ra : rb;
-            if (c + 1 < kTile / kChunk) {
+            if (c + 1 < kSpan / kChunk) {
               ptx::tmem_ld<kChunk>(taddr + (c + 1) * kChunk, nxt);
             } else {
-              // every lane holds the rest of the tile: hand the accumulator back
+              // every lane holds the rest of its span: hand the accumulator back
               ptx::tc_fence_before_sync();
               __syncwarp();
               if (lane == 0) ptx::mbar_arrive(bar_tm_empty(a, ts));
@@ -532,12 +634,11 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
               consume(cur, c);
               PROF_ADD(34);
             }
-            if (c + 1 < kTile / kChunk) {
+            if (c + 1 < kSpan / kChunk) {
               PROF_T0();
               ptx::tmem_ld_wait<kChunk>(nxt);
               PROF_ADD(35);
             }
-          }
           }
           ++tm_seq;
         }
@@ -548,25 +649,61 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
       }
       ring_base += (uint32_t)(g.c_hi - g.c_lo);
       if (!ok) break;
+      if (PHASE == PH_DUMP || g.r0[a] >= p.LS) continue;  // nothing to write for this sub-tile
 
       // ------------------------------------------------------ item epilogue
+      // The kColSplit threads that share a row / column combine their partial
+      // state through shared memory; the thread of part 0 writes the result.
+      float v0, v1 = 0.f;
       if (PHASE == PH_ROWS) {
-        if (mine < p.M && g.r0[a] < p.LS) {
+        v0 = m_run;
+        v1 = l_run;
+      } else if (RED == RED_SUM) {
+        v0 = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+      } else {
+        v0 = fmaxf(fmaxf(acc[0], acc[1]), fmaxf(acc[2], acc[3]));
+      }
+      if (kColSplit > 1) {
+        const uint32_t slot = merge_seq & 1u, mph = (merge_seq >> 1) & 1u;
+        float2* cell = merge_buf + ((size_t)slot * kSubTiles + a) * kTile + tid_wg;
+        ++merge_seq;
+        if (part != 0) {
+          ok = WAIT(bar_merge_empty(a, slot), mph ^ 1u, ST_WAIT_MERGE_EMPTY);
+          if (!ok) break;
+          *cell = make_float2(v0, v1);
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive(bar_merge_full(a, slot));
+          continue;
+        }
+        ok = WAIT(bar_merge_full(a, slot), mph, ST_WAIT_MERGE_FULL);
+        if (!ok) break;
+        const float2 other = *cell;
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(bar_merge_empty(a, slot));
+        if (PHASE == PH_ROWS) {
+          const float mx = fmaxf(v0, other.x);
+          const float ms = (mx == -INFINITY) ? 0.f : mx;
+          v1 = v1 * ptx::ex2(v0 - ms) + other.y * ptx::ex2(other.x - ms);
+          v0 = mx;
+        } else if (RED == RED_SUM) {
+          v0 += other.x;
+        } else {
+          v0 = fmaxf(v0, other.x);
+        }
+      }
+      if (PHASE == PH_ROWS) {
+        if (mine < p.M) {
           if (p.n_split == 1) {
-            p.neg_lse[(size_t)g.bh * p.m_pad + mine] = -(m_run + log2f(l_run));
+            p.neg_lse[(size_t)g.bh * p.m_pad + mine] = -(v0 + log2f(v1));
           } else {
             const size_t idx = ((size_t)g.sp * p.BH + g.bh) * p.m_pad + mine;
-            p.part_m[idx] = m_run;
-            p.part_l[idx] = l_run;
+            p.part_m[idx] = v0;
+            p.part_l[idx] = v1;
           }
         }
       } else if (PHASE == PH_COLS) {
         if (mine < p.N) {
-          float v;
-          if (RED == RED_SUM)
-            v = (acc[0] + acc[1]) + (acc[2] + acc[3]);
-          else
-            v = ptx::ex2(fmaxf(fmaxf(acc[0], acc[1]), fmaxf(acc[2], acc[3])));
+          float v = (RED == RED_SUM) ? v0 : ptx::ex2(v0);
           if (p.n_split == 1) {
             if (p.mean_mode) v = v / mean_divisor(p, mine);
             store_out(p.out, p.out_dtype, (size_t)g.bh * p.N + mine, v);
@@ -824,6 +961,7 @@ static void fill_common(PassParams& pp, const fcr_problem& pr, const fcr_plan& p
   pp.part_l = reinterpret_cast<float*>(ws + pl.off_part_l);
   pp.part_out = reinterpret_cast<float*>(ws + pl.off_part_out);
   pp.status = reinterpret_cast<int*>(ws + pl.off_status);
+  pp.sched_counter = pp.status + (cols ? 9 : 8);
 }
 
 static void fill_mean(PassParams& pp, int reduction, int is_causal, int M, int N) {
@@ -853,6 +991,11 @@ int fcr_plan_problem(const fcr_problem* problem, int32_t num_sms, fcr_plan* plan
   std::string err;
   const int rc = plan_problem(*problem, sms, *plan, err);
   if (rc != FCR_OK) return fail(rc, err);
+  // Tuning knob: FCR_HEAD_GROUP overrides how many heads share the L2 cache.
+  if (const char* hg = getenv("FCR_HEAD_GROUP")) {
+    const int v = atoi(hg);
+    if (v >= 1) plan->head_group = std::min(v, problem->B * problem->H);
+  }
   return FCR_OK;
 }
 

@@ -33,6 +33,7 @@ struct PassGeom {
   int n_split;     // splits of the streamed range
   int n_items;     // BH * n_sb * n_split
   int sb_reverse;  // heaviest blocks first
+  int head_group;  // heads whose items are interleaved (their Q and K share the L2 cache)
 };
 
 // One work item: a head, a block of two stationary 128-row tiles, one split of
@@ -58,11 +59,19 @@ FCR_HD T hd_max(T a, T b) { return a > b ? a : b; }
 // per 64-row program, flash_colreduce/flash.py:201-207).
 template <bool COLS>
 FCR_HD Item decode_item(const PassGeom& p, int item) {
+  // Item order: groups of `head_group` heads; inside a group the stationary
+  // blocks run heaviest first and the heads of the group are interleaved, so
+  // that concurrently running CTAs work on few heads (L2 reuse of the streamed
+  // operand) while the work handed out last is the lightest (short tail).
   Item g;
   const int sp = item % p.n_split;
   const int rest = item / p.n_split;
-  const int o = rest % p.n_sb;
-  g.bh = rest / p.n_sb;
+  const int per_group = p.head_group * p.n_sb;
+  const int grp = rest / per_group;
+  const int in_grp = rest - grp * per_group;
+  const int heads_here = hd_min(p.head_group, p.BH - grp * p.head_group);
+  const int o = in_grp / heads_here;
+  g.bh = grp * p.head_group + (in_grp - o * heads_here);
   g.sp = sp;
   const int sb = p.sb_reverse ? (p.n_sb - 1 - o) : o;
   int lo = 0x7fffffff, hi = 0;
@@ -203,6 +212,14 @@ inline int plan_problem(const fcr_problem& p, int num_sms, fcr_plan& pl, std::st
   }
   pl.row_items = (int32_t)row_items;
   pl.col_items = (int32_t)col_items;
+  // With the causal mask the items of a head shrink towards its end: interleave the
+  // heads whose Q and K (fp16) fit a 40 MiB share of the L2 cache together (16 at most),
+  // so that the tail of the grid is made of the lightest items of many heads.  Without
+  // the mask all items weigh the same and one head at a time keeps the CTAs in step.
+  const int64_t head_bytes = ((int64_t)p.M + p.N) * pl.d_pad * 2;
+  pl.head_group = !causal ? 1
+                          : (int32_t)std::max<int64_t>(
+                                1, std::min<int64_t>(std::min<int64_t>(BH, 16), (40LL << 20) / head_bytes));
   pl.row_ctas = (int32_t)std::min<int64_t>(row_items, num_sms);
   pl.col_ctas = (int32_t)std::min<int64_t>(col_items, num_sms);
 
@@ -249,6 +266,7 @@ inline PassGeom pass_geometry(const fcr_problem& p, const fcr_plan& pl, bool col
   g.n_split = cols ? pl.col_splits : pl.row_splits;
   g.n_items = cols ? pl.col_items : pl.row_items;
   g.sb_reverse = (!cols && g.causal) ? 1 : 0;  // rows pass: late blocks see the most keys
+  g.head_group = pl.head_group;
   return g;
 }
 

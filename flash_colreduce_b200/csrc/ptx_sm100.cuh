@@ -159,6 +159,34 @@ __device__ __forceinline__ float lg2(float x) {
   return y;
 }
 
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float y;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(y) : "f"(a), "f"(b), "f"(c));
+  return y;
+}
+// 2^x for a pair of values on the FMA and integer pipes instead of MUFU:
+// x = n + f with n = round(x) (magic-number rounding), f in [-0.5, 0.5],
+// 2^f by a degree-4 minimax polynomial (relative error 2.7e-6), and n added
+// into the exponent field.  Inputs are clamped at -126 so that the exponent
+// cannot wrap; the result for anything below is 2^-126 (practically zero).
+__device__ __forceinline__ float2 ex2_poly2(float2 x) {
+  const float kMagic = 12582912.0f;  // 1.5 * 2^23
+  x.x = fmaxf(x.x, -126.f);
+  x.y = fmaxf(x.y, -126.f);
+  const float2 t = __fadd2_rn(x, make_float2(kMagic, kMagic));
+  const float2 n = __fadd2_rn(t, make_float2(-kMagic, -kMagic));
+  const float2 f = __fadd2_rn(x, make_float2(-n.x, -n.y));
+  float2 p = __ffma2_rn(f, make_float2(0.009570101753f, 0.009570101753f),
+                        make_float2(0.05591786031f, 0.05591786031f));
+  p = __ffma2_rn(p, f, make_float2(0.2402474483f, 0.2402474483f));
+  p = __ffma2_rn(p, f, make_float2(0.6931218147f, 0.6931218147f));
+  p = __ffma2_rn(p, f, make_float2(0.9999992614f, 0.9999992614f));
+  float2 r;
+  r.x = __int_as_float(__float_as_int(p.x) + (__float_as_int(t.x) << 23));
+  r.y = __int_as_float(__float_as_int(p.y) + (__float_as_int(t.y) << 23));
+  return r;
+}
+
 // ------------------------------------------------- tcgen05 descriptor helpers
 // Shared-memory matrix descriptor for a K-major operand tile stored as rows of
 // 128 bytes with the 128-byte swizzle (what a TMA box of 64 fp16 x rows with
