@@ -28,6 +28,7 @@ EXPORTS = (
     "fcr_plan_item",
     "fcr_workspace_bytes",
     "fcr_colreduce",
+    "fcr_colreduce_static",
     "fcr_finalize",
     "fcr_read_device_status",
     "fcr_trace_enable",
@@ -92,6 +93,9 @@ def _load() -> C.CDLL:
     lib.fcr_colreduce.argtypes = [C.POINTER(Problem), C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32,
                                   C.c_void_p, C.c_size_t, C.c_void_p]
     lib.fcr_colreduce.restype = C.c_int
+    lib.fcr_colreduce_static.argtypes = [C.POINTER(Problem), C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32,
+                                         C.c_void_p]
+    lib.fcr_colreduce_static.restype = C.c_int
     lib.fcr_finalize.argtypes = [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
                                  C.c_int32, C.c_int32, C.c_int32, C.c_void_p]
     lib.fcr_finalize.restype = C.c_int

@@ -34,6 +34,7 @@
 #include <string.h>
 
 #include <array>
+#include <mutex>
 #include <string>
 #include <vector>
 
@@ -1176,6 +1177,64 @@ int fcr_debug_scores(const fcr_problem* problem, const void* q, const void* k, f
   if (rc != FCR_OK) return rc;
   const int ctas = std::min(pp.n_items, sms);
   return launch_pass_d<PH_DUMP, RED_SUM>(pl.d_pad, map_q, map_k, pp, ctas, stream);
+}
+
+// ----------------------------------------------------------------------
+// Operator for callers that may not allocate device memory.
+//
+// Some hosts of this library never get to call cudaMalloc: a plugin running
+// inside another runtime's enqueue hook (the runtime owns every byte of the
+// device and forbids allocation there), a serving loop that reserved its whole
+// memory budget up front, or code that must not touch an allocator because the
+// surrounding framework's caching allocator is locked or not reachable from C.
+// For them the workspace fcr_colreduce needs lives in the library image
+// itself: a fixed array in device global memory, present on every GPU that
+// loads the library for as long as the process runs.
+constexpr size_t kStaticScratchBytes = FCR_STATIC_SCRATCH_BYTES;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+// In host code `g_static_scratch` is only a handle for the symbol, not a
+// device address, so the address is looked up once per device (with that
+// device current) and remembered.
+static std::mutex g_scratch_mutex;
+static void* g_scratch_addr[64] = {};
+
+static int static_scratch_address(void** out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+  if (dev < 0 || dev >= 64) return fail(FCR_ERR_UNSUPPORTED, "device ordinal beyond 63");
+  std::lock_guard<std::mutex> lock(g_scratch_mutex);
+  if (!g_scratch_addr[dev]) {
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(static scratch)");
+    if (!ptr) return fail(FCR_ERR_CUDA, "cudaGetSymbolAddress returned a null address");
+    g_scratch_addr[dev] = ptr;
+  }
+  *out = g_scratch_addr[dev];
+  return FCR_OK;
+}
+
+int fcr_colreduce_static(const fcr_problem* problem, const void* q, const void* k, void* out,
+                         int32_t out_dtype, void* stream_v) {
+  if (!problem || !q || !k || !out) return fail(FCR_ERR_BAD_ARG, "null argument");
+  fcr_plan pl;
+  int rc = fcr_plan_problem(problem, 0, &pl);
+  if (rc != FCR_OK) return rc;
+  if ((size_t)pl.workspace_bytes > kStaticScratchBytes)
+    return fail(FCR_ERR_WORKSPACE,
+                "this problem needs " + std::to_string(pl.workspace_bytes) +
+                    " bytes of scratch but the built-in scratch holds " +
+                    std::to_string(kStaticScratchBytes) +
+                    " (FCR_STATIC_SCRATCH_BYTES); use fcr_colreduce with a caller-owned workspace");
+  void* scratch = nullptr;
+  rc = static_scratch_address(&scratch);
+  if (rc != FCR_OK) return rc;
+  // Same kernels as fcr_colreduce, handed the built-in array.  The status words
+  // and scheduler counters at its start are cleared on the stream by that call;
+  // everything else in the array is written before it is read.
+  return fcr_colreduce(problem, q, k, out, out_dtype, scratch, kStaticScratchBytes, stream_v);
 }
 
 double fcr_probe_ex2_rate(int32_t repeats) {

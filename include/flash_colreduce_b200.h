@@ -148,6 +148,39 @@ int fcr_colreduce(const fcr_problem* problem, const void* q, const void* k, void
                   int32_t out_dtype, void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * The operator without a caller-supplied workspace and without any allocation.
+ * (No counterpart in the reference, which allocates through PyTorch,
+ * flash_colreduce/flash.py:286.)
+ *
+ * Meant for hosts that cannot call cudaMalloc where this library runs: a
+ * plugin invoked from another runtime's enqueue hook, a process that handed
+ * its whole device-memory budget to one arena at start-up, or C code that has
+ * no route to the framework allocator that owns the device.  The scratch
+ * memory the kernels need (status words, per-row log-sum-exp, split partials)
+ * is a fixed FCR_STATIC_SCRATCH_BYTES array in device global memory inside the
+ * library image: every GPU that loads the library holds that much until the
+ * process exits.
+ *
+ * - q, k, out, out_dtype, stream: exactly as for fcr_colreduce; the caller
+ *   still owns inputs and output.
+ * - A problem whose fcr_workspace_bytes() exceeds FCR_STATIC_SCRATCH_BYTES is
+ *   rejected with FCR_ERR_WORKSPACE and a message naming both numbers.
+ * - The first call on each device looks up the array's device address (with
+ *   that device current) and caches it; make that first call before any
+ *   stream capture begins.
+ * - All calls share the one array and it keeps whatever the previous call left
+ *   in it.  The call clears the words that must start at zero on `stream`
+ *   itself, so back-to-back calls on one stream are fine; two calls that can
+ *   overlap on the GPU (different streams, or different host threads on
+ *   different streams) race on the array and must be serialised by the caller.
+ * - Performs no cudaMalloc / cudaFree and uses no allocating library routine
+ *   (tracing, if enabled with fcr_trace_enable, creates CUDA events: leave it off).
+ */
+#define FCR_STATIC_SCRATCH_BYTES (8u << 20)
+int fcr_colreduce_static(const fcr_problem* problem, const void* q, const void* k, void* out,
+                         int32_t out_dtype, void* stream);
+
+/*
  * Tail of a sharded run: `acc` holds fp32 column sums (or maxima) of shape
  * (B,H,N) that were produced with reduction FCR_SUM / FCR_MAX and combined
  * across shards; this applies the mean divisor (for FCR_MEAN) for a whole
