@@ -57,15 +57,22 @@ constexpr int kMmaWarps = kSubTiles;          // one issuing warp per stationary
 constexpr int kThreads = (kSoftmaxWarps + 1 + kMmaWarps) * 32;
 constexpr int kTmemCols = 512;
 constexpr int kSpan = kTile / kColSplit;      // accumulator columns of a tile one softmax thread folds
-#ifndef FCR_CHUNK
-#define FCR_CHUNK 32
+#ifndef FCR_CHUNK_ROWS
+#define FCR_CHUNK_ROWS 64
 #endif
-constexpr int kChunk = FCR_CHUNK;             // columns per tensor-memory load
+#ifndef FCR_CHUNK_COLS
+#define FCR_CHUNK_COLS 32
+#endif
+// accumulator columns per tensor-memory load: one load per tile in the rows pass (one
+// running-max update per 64 keys), two in the columns pass (the lse operands cost registers)
+constexpr int kChunkRows = FCR_CHUNK_ROWS;
+constexpr int kChunkCols = FCR_CHUNK_COLS;
 #ifndef FCR_POLY
 #define FCR_POLY 2
 #endif
 constexpr int kPolyOf8 = FCR_POLY;            // exponentials per 8 taken off the MUFU pipe (0, 2, 4, 6)
-static_assert(kSpan % kChunk == 0 && kChunk % 32 == 0, "chunk must divide the per-thread span");
+static_assert(kSpan % kChunkRows == 0 && kChunkRows % 32 == 0 && kSpan % kChunkCols == 0 &&
+                  kChunkCols % 32 == 0, "chunk must divide the per-thread span");
 constexpr long long kWaitLimitCycles = 2000000000LL;  // about one second
 
 // Device status codes (status word 0).  Word 1: block, word 2: thread, word 3: detail.
@@ -230,6 +237,23 @@ __device__ __forceinline__ void rows_chunk(const uint32_t* r, float scale2, int 
   const float m_safe = (m_new == -INFINITY) ? 0.f : m_new;  // row sees nothing yet
   const float alpha = ptx::ex2(m_run - m_safe);
   const float nm = -m_safe;
+#ifdef FCR_SCALAR
+  float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+#pragma unroll
+  for (int e = 0; e < W; e += 4) {
+    float t[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      t[u] = fmaf(x[e + u], scale2, nm);
+      if (!MASKED && ((e + u) & 7) < kPolyOf8) t[u] = ptx::ex2_poly(t[u]);
+      else t[u] = ptx::ex2(t[u]);
+    }
+    s0 += t[0]; s1 += t[1]; s2 += t[2]; s3 += t[3];
+  }
+  l_run = fmaf(l_run, alpha, (s0 + s1) + (s2 + s3));
+  m_run = m_new;
+  return;
+#endif
   float2 s01 = make_float2(0.f, 0.f), s23 = make_float2(0.f, 0.f);
 #pragma unroll
   for (int e = 0; e < W; e += 4) {
@@ -265,6 +289,28 @@ __device__ __forceinline__ void rows_chunk(const uint32_t* r, float scale2, int 
 template <int RED, bool MASKED, int W>
 __device__ __forceinline__ void cols_chunk(const uint32_t* r, const float* neg_lse,
                                            float scale2, int e_lo, int e_hi, float (&acc)[4]) {
+#ifdef FCR_SCALAR
+#pragma unroll
+  for (int q = 0; q < W / 4; ++q) {
+    const float4 nl = reinterpret_cast<const float4*>(neg_lse)[q];
+    const float nlv[4] = {nl.x, nl.y, nl.z, nl.w};
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int e = q * 4 + u;
+      float t = fmaf(__uint_as_float(r[e]), scale2, nlv[u]);
+      const bool valid = !MASKED || (e >= e_lo && e < e_hi);
+      if (RED == RED_SUM) {
+        float pr = (!MASKED && (e & 7) < kPolyOf8) ? ptx::ex2_poly(t) : ptx::ex2(t);
+        if (MASKED) pr = valid ? pr : 0.f;
+        acc[u] += pr;
+      } else {
+        if (MASKED) t = valid ? t : -INFINITY;
+        acc[u] = fmaxf(acc[u], t);
+      }
+    }
+  }
+  return;
+#endif
 #pragma unroll
   for (int q = 0; q < W / 4; ++q) {
     const float4 nl = reinterpret_cast<const float4*>(neg_lse)[q];
@@ -589,7 +635,8 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
           const float* lse_s =
               reinterpret_cast<const float*>(smem + L::off_lse + s * L::kLseBytes) + col_base;
 
-          uint32_t ra[kChunk], rb[kChunk];
+          constexpr int kChunk = (PHASE == PH_COLS) ? kChunkCols : kChunkRows;
+          uint32_t ra[kChunk];
           auto consume = [&](const uint32_t* r, int c) {
             if constexpr (PHASE == PH_DUMP) {
               float4* dst = reinterpret_cast<float4*>(
@@ -611,6 +658,21 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
                 cols_chunk<RED, false, kChunk>(r, lse_s + kChunk * c, p.scale2, 0, kChunk, acc);
             }
           };
+#ifndef FCR_DOUBLEBUF
+          // one chunk at a time: the other warps of the scheduler cover the load latency
+#pragma unroll
+          for (int c = 0; c < kSpan / kChunk; ++c) {
+            ptx::tmem_ld<kChunk>(taddr + c * kChunk, ra);
+            ptx::tmem_ld_wait<kChunk>(ra);
+            if (c + 1 == kSpan / kChunk) {
+              ptx::tc_fence_before_sync();
+              __syncwarp();
+              if (lane == 0) ptx::mbar_arrive(bar_tm_empty(a, ts));
+            }
+            consume(ra, c);
+          }
+#else
+          uint32_t rb[kChunk];
           // chunk c+1 is in flight from tensor memory while chunk c is folded
           {
             PROF_T0();
@@ -641,6 +703,7 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
               PROF_ADD(35);
             }
           }
+#endif
           ++tm_seq;
         }
         if (PHASE == PH_COLS) {
