@@ -19,7 +19,7 @@ LIB_NAME = "libflash_colreduce_b200.so"
 LIB_PATH = os.path.join(LIB_DIR, LIB_NAME)
 
 SOURCES = ["colreduce_sm100.cu"]
-HEADERS = ["ptx_sm100.cuh", "plan.h", os.path.join("..", "..", "include", "flash_colreduce_b200.h")]
+HEADERS = ["ptx_sm100.cuh", "softmax_fold.cuh", "plan.h", os.path.join("..", "..", "include", "flash_colreduce_b200.h")]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

@@ -30,16 +30,22 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
                : "memory");
 }
+#ifndef FCR_WAIT_HINT_NS
+#define FCR_WAIT_HINT_NS 20000
+#endif
+// One attempt at waiting for the phase with the given parity.  The hint lets
+// the hardware keep the thread suspended (issuing nothing) for up to that many
+// nanoseconds or until the phase completes, whichever comes first.
 __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t done;
   asm volatile(
       "{\n\t"
       ".reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t"
       "}"
       : "=r"(done)
-      : "r"(bar), "r"(parity)
+      : "r"(bar), "r"(parity), "r"((uint32_t)FCR_WAIT_HINT_NS)
       : "memory");
   return done;
 }
