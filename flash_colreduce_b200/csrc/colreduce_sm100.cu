@@ -450,10 +450,25 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
       float acc[4];
 #pragma unroll
       for (int u = 0; u < 4; ++u) acc[u] = (RED == RED_MAX) ? -INFINITY : 0.f;
+      // Per item: the streamed indices this thread's row / column may use, [valid_lo, valid_hi),
+      // and which tiles intersect a mask edge (all others take the unmasked code path).
+      int valid_lo = 0, valid_hi, mask_from, mask_until = 0;
+      if (PHASE == PH_COLS) {
+        // queries i with max(mine - off, 0) <= i < M attend key `mine`
+        valid_lo = p.causal ? max(mine - p.off, 0) : 0;
+        valid_hi = p.M;
+        mask_from = p.M >> 7;  // the ragged last tile, if any
+        mask_until = p.causal ? max(g.r0[a] + 2 * kTile - 2 - p.off, 0) >> 7 : 0;  // diagonal tiles
+      } else {
+        // keys j <= min(N - 1, mine + off) are attended by query `mine`
+        valid_hi = p.causal ? (int)min((long long)p.N, (long long)mine + p.off + 1) : p.N;
+        mask_from = p.N >> 7;
+        if (p.causal) mask_from = (int)min((long long)mask_from, ((long long)g.r0[a] + p.off + 1) >> 7);
+      }
 
-      for (int t = g.c_lo; ok && t < g.c_hi; ++t) {
+      uint32_t rs = ring_base;
+      for (int t = g.c_lo; ok && t < g.c_hi; ++t, ++rs) {
         const bool active = (t >= g.t_lo[a]) && (t < g.t_hi[a]);
-        const uint32_t rs = ring_base + (uint32_t)(t - g.c_lo);
         const uint32_t s = rs % KR, rph = (rs / KR) & 1u;
         if (PHASE == PH_COLS) {
           ok = WAIT(bar_ring_full(s), rph, ST_WAIT_RING_FULL_SM);
@@ -467,23 +482,8 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
           const uint32_t taddr =
               tmem_base + lane_field + (uint32_t)(a * 2 + ts) * kTile + (uint32_t)col_base;
           const int c0 = t * kTile + col_base;  // streamed index of this thread's first column
-          bool need_mask;
-          int lim_lo = 0, lim_hi = 0;
-          if (PHASE == PH_COLS) {
-            // valid queries i: max(mine - off, 0) <= i < M
-            need_mask = (t * kTile + kTile > p.M) ||
-                        (p.causal && (t * kTile + p.off < g.r0[a] + kTile - 1));
-            lim_lo = p.causal ? max(mine - p.off, 0) - c0 : -(1 << 30);
-            lim_hi = p.M - c0;
-          } else {
-            // valid keys j: j <= min(N - 1, mine + off)
-            need_mask = (t * kTile + kTile > p.N) ||
-                        (p.causal && (t * kTile + kTile - 1 > g.r0[a] + p.off));
-            const long long jlim =
-                p.causal ? min((long long)p.N - 1, (long long)mine + p.off) : (long long)p.N - 1;
-            lim_hi = (int)max(min(jlim - c0 + 1, (long long)(1 << 20)), (long long)-(1 << 20));
-          }
-          if (PHASE == PH_DUMP) need_mask = false;
+          const bool need_mask = (PHASE != PH_DUMP) && (t >= mask_from || t < mask_until);
+          const int lim_lo = valid_lo - c0, lim_hi = valid_hi - c0;
           const float* lse_s =
               reinterpret_cast<const float*>(smem + L::off_lse + s * L::kLseBytes) + col_base;
 
