@@ -514,14 +514,22 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
           // one chunk at a time: the other warps of the scheduler cover the load latency
 #pragma unroll
           for (int c = 0; c < kSpan / kChunk; ++c) {
-            ptx::tmem_ld<kChunk>(taddr + c * kChunk, ra);
-            ptx::tmem_ld_wait<kChunk>(ra);
+            {
+              PROF_T0();
+              ptx::tmem_ld<kChunk>(taddr + c * kChunk, ra);
+              ptx::tmem_ld_wait<kChunk>(ra);
+              PROF_ADD(33);
+            }
             if (c + 1 == kSpan / kChunk) {
               ptx::tc_fence_before_sync();
               __syncwarp();
               if (lane == 0) ptx::mbar_arrive(bar_tm_empty(a, ts));
             }
-            consume(ra, c);
+            {
+              PROF_T0();
+              consume(ra, c);
+              PROF_ADD(34);
+            }
           }
 #else
           uint32_t rb[kChunk];

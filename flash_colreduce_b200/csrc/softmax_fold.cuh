@@ -19,7 +19,7 @@ constexpr int kPolyOf8 = FCR_POLY;  // exponentials per 8 taken off the MUFU pip
 // One 32-column chunk of a query row: online max / sum in the base-2 domain
 // (flash_colreduce/flash.py:71-78).  `nvalid` = number of leading columns of
 // the chunk this row may attend (only read when MASKED).
-template <bool MASKED, int W>
+template <bool MASKED, int W, int POLY = kPolyOf8>
 __device__ __forceinline__ void rows_chunk(const uint32_t* r, float scale2, int nvalid,
                                            float& m_run, float& l_run) {
   float x[W];
@@ -48,7 +48,7 @@ __device__ __forceinline__ void rows_chunk(const uint32_t* r, float scale2, int 
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
       t[u] = fmaf(x[e + u], scale2, nm);
-      if (!MASKED && ((e + u) & 7) < kPolyOf8) t[u] = ptx::ex2_poly(t[u]);
+      if (!MASKED && ((e + u) & 7) < POLY) t[u] = ptx::ex2_poly(t[u]);
       else t[u] = ptx::ex2(t[u]);
     }
     s0 += t[0]; s1 += t[1]; s2 += t[2]; s3 += t[3];
@@ -65,13 +65,13 @@ __device__ __forceinline__ void rows_chunk(const uint32_t* r, float scale2, int 
     float2 a23 = __ffma2_rn(make_float2(x[e + 2], x[e + 3]), make_float2(scale2, scale2),
                             make_float2(nm, nm));
     // kPolyOf8 of every 8 exponentials are evaluated on the FMA pipe (never in masked tiles)
-    if (!MASKED && (e & 7) < kPolyOf8) {
+    if (!MASKED && (e & 7) < POLY) {
       a01 = ptx::ex2_poly2(a01);
     } else {
       a01.x = ptx::ex2(a01.x);
       a01.y = ptx::ex2(a01.y);
     }
-    if (!MASKED && ((e + 2) & 7) < kPolyOf8) {
+    if (!MASKED && ((e + 2) & 7) < POLY) {
       a23 = ptx::ex2_poly2(a23);
     } else {
       a23.x = ptx::ex2(a23.x);
@@ -89,7 +89,7 @@ __device__ __forceinline__ void rows_chunk(const uint32_t* r, float scale2, int 
 // the column's accumulators (flash_colreduce/flash.py:120-124).  Queries
 // e in [e_lo, e_hi) of the chunk are valid (only read when MASKED).  For max
 // the fold is done on the exponent, exp2 being monotonic.
-template <int RED, bool MASKED, int W>
+template <int RED, bool MASKED, int W, int POLY = kPolyOf8>
 __device__ __forceinline__ void cols_chunk(const uint32_t* r, const float* neg_lse,
                                            float scale2, int e_lo, int e_hi, float (&acc)[4]) {
 #ifdef FCR_SCALAR
@@ -103,7 +103,7 @@ __device__ __forceinline__ void cols_chunk(const uint32_t* r, const float* neg_l
       float t = fmaf(__uint_as_float(r[e]), scale2, nlv[u]);
       const bool valid = !MASKED || (e >= e_lo && e < e_hi);
       if (RED == RED_SUM) {
-        float pr = (!MASKED && (e & 7) < kPolyOf8) ? ptx::ex2_poly(t) : ptx::ex2(t);
+        float pr = (!MASKED && (e & 7) < POLY) ? ptx::ex2_poly(t) : ptx::ex2(t);
         if (MASKED) pr = valid ? pr : 0.f;
         acc[u] += pr;
       } else {
@@ -124,13 +124,13 @@ __device__ __forceinline__ void cols_chunk(const uint32_t* r, const float* neg_l
                             make_float2(scale2, scale2), make_float2(nl.z, nl.w));
     if (RED == RED_SUM) {
       // kPolyOf8 of every 8 exponentials are evaluated on the FMA pipe (never in masked tiles)
-      if (!MASKED && (e & 7) < kPolyOf8) {
+      if (!MASKED && (e & 7) < POLY) {
         t01 = ptx::ex2_poly2(t01);
       } else {
         t01.x = ptx::ex2(t01.x);
         t01.y = ptx::ex2(t01.y);
       }
-      if (!MASKED && ((e + 2) & 7) < kPolyOf8) {
+      if (!MASKED && ((e + 2) & 7) < POLY) {
         t23 = ptx::ex2_poly2(t23);
       } else {
         t23.x = ptx::ex2(t23.x);
@@ -142,10 +142,13 @@ __device__ __forceinline__ void cols_chunk(const uint32_t* r, const float* neg_l
         t23.x = (e + 2 >= e_lo && e + 2 < e_hi) ? t23.x : 0.f;
         t23.y = (e + 3 >= e_lo && e + 3 < e_hi) ? t23.y : 0.f;
       }
-      acc[0] += t01.x;
-      acc[1] += t01.y;
-      acc[2] += t23.x;
-      acc[3] += t23.y;
+      // packed adds: acc[0..1] and acc[2..3] are two register pairs
+      const float2 a01 = __fadd2_rn(make_float2(acc[0], acc[1]), t01);
+      const float2 a23 = __fadd2_rn(make_float2(acc[2], acc[3]), t23);
+      acc[0] = a01.x;
+      acc[1] = a01.y;
+      acc[2] = a23.x;
+      acc[3] = a23.y;
     } else {
       if (MASKED) {
         t01.x = (e >= e_lo && e < e_hi) ? t01.x : -INFINITY;
