@@ -56,7 +56,15 @@ constexpr int kMmaWarp = kSoftmaxWarps + 1;   // issues the MMAs of sub-tile 0, 
 constexpr int kMmaWarps = kSubTiles;          // one issuing warp per stationary sub-tile
 constexpr int kThreads = (kSoftmaxWarps + 1 + kMmaWarps) * 32;
 constexpr int kTmemCols = 512;
-constexpr int kSpan = kTile / kColSplit;      // accumulator columns of a tile one softmax thread folds
+#ifndef FCR_TILE_OWNER
+#define FCR_TILE_OWNER 1
+#endif
+// How the kColSplit softmax warpgroups of a stationary sub-tile share its accumulator tiles:
+// true: they take whole tiles in turn (warpgroup p folds the tiles in buffer p), which keeps
+// them independent of each other; false: every tile is split by column ranges.
+constexpr bool kTileOwner = FCR_TILE_OWNER != 0;
+static_assert(!kTileOwner || kColSplit == 2, "tile ownership alternates between two warpgroups");
+constexpr int kSpan = kTileOwner ? kTile : kTile / kColSplit;  // columns of a tile one thread folds
 #ifndef FCR_CHUNK_ROWS
 #define FCR_CHUNK_ROWS 64
 #endif
@@ -262,12 +270,14 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
     }
     for (int i = 0; i < KR; ++i) {
       ptx::mbar_init(bar_ring_full(i), 1);
-      ptx::mbar_init(bar_ring_empty(i), PHASE == PH_COLS ? kMmaWarps + kSoftmaxWarps : kMmaWarps);
+      ptx::mbar_init(bar_ring_empty(i),
+                     PHASE != PH_COLS ? kMmaWarps
+                                      : kMmaWarps + (kTileOwner ? 4 * kSubTiles : kSoftmaxWarps));
     }
     for (int a = 0; a < 2; ++a)
       for (int ts = 0; ts < 2; ++ts) {
         ptx::mbar_init(bar_tm_full(a, ts), 1);
-        ptx::mbar_init(bar_tm_empty(a, ts), 4 * kColSplit);
+        ptx::mbar_init(bar_tm_empty(a, ts), kTileOwner ? 4 : 4 * kColSplit);
         ptx::mbar_init(bar_merge_full(a, ts), kColSplit > 1 ? 4 * (kColSplit - 1) : 1);
         ptx::mbar_init(bar_merge_empty(a, ts), 4);
       }
@@ -361,7 +371,11 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
     // handshakes overlap the other's MMAs.
     PROF_DECL();
     const int a = warp - kMmaWarp;
-    uint32_t ring_seq = 0, item_seq = 0, tm_seq = 0;
+    // Accumulator buffer of a tile = its index within the work item, mod 2 (so that the
+    // warpgroup that folds it does not depend on which items this CTA happened to get);
+    // tm_use[b] counts the uses of buffer b and gives its barrier phase.
+    uint32_t ring_seq = 0, item_seq = 0;
+    uint32_t tm_use[2] = {0, 0};
     bool ok = true;
     for (;; ++item_seq) {
       const uint32_t si = item_seq % KI, sph = (item_seq / KI) & 1u;
@@ -382,7 +396,8 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
         ok = WAIT(bar_ring_full(s), ph, ST_WAIT_RING_FULL);
         if (!ok) break;
         if (t >= g.t_lo[a] && t < g.t_hi[a]) {
-          const uint32_t ts = tm_seq & 1u, tph = (tm_seq >> 1) & 1u;
+          const uint32_t ts = (uint32_t)(t - g.t_lo[a]) & 1u;
+          const uint32_t tph = (ts ? tm_use[1] : tm_use[0]) & 1u;
           ok = WAIT(bar_tm_empty(a, ts), tph ^ 1u, ST_WAIT_TMEM_EMPTY);
           if (!ok) break;
           ptx::tc_fence_after_sync();
@@ -401,7 +416,7 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
           }
           __syncwarp();
           PROF_ADD(25);
-          ++tm_seq;
+          if (ts) ++tm_use[1]; else ++tm_use[0];
         } else {
           // not this sub-tile's tile: the slot is released as soon as it has been filled
           if (lane == 0) ptx::mbar_arrive(bar_ring_empty(s));
@@ -432,9 +447,10 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
     const int part = warp / (4 * kSubTiles);
     const int tid_wg = (warp & 3) * 32 + lane;
     const uint32_t lane_field = (uint32_t)((warp & 3) * 32) << 16;
-    const int col_base = part * kSpan;  // first accumulator column this thread folds
+    const int col_base = kTileOwner ? 0 : part * kSpan;  // first accumulator column this thread folds
     float2* merge_buf = reinterpret_cast<float2*>(smem + L::off_merge);
-    uint32_t ring_base = 0, tm_seq = 0, merge_seq = 0;
+    uint32_t ring_base = 0, merge_seq = 0;
+    uint32_t tm_use[2] = {0, 0};  // uses of each accumulator buffer of sub-tile a seen by this warp
     bool ok = true;
     for (uint32_t item_seq = 0;; ++item_seq) {
       const uint32_t si = item_seq % KI, sph = (item_seq / KI) & 1u;
@@ -468,14 +484,22 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
 
       uint32_t rs = ring_base;
       for (int t = g.c_lo; ok && t < g.c_hi; ++t, ++rs) {
-        const bool active = (t >= g.t_lo[a]) && (t < g.t_hi[a]);
+        const bool in_range = (t >= g.t_lo[a]) && (t < g.t_hi[a]);
+        const uint32_t ts = (uint32_t)(t - g.t_lo[a]) & 1u;  // accumulator buffer of this tile
+        // with tile ownership a warpgroup folds every other tile of its sub-tile
+        const bool active = in_range && (!kTileOwner || (int)ts == part);
         const uint32_t s = rs % KR, rph = (rs / KR) & 1u;
-        if (PHASE == PH_COLS) {
+        // columns pass: the ring slot also carries the tile's lse values; it is released by the
+        // warps that read them (or, for a tile the sub-tile skips, by the warpgroup of its parity)
+        const bool holds_slot =
+            PHASE == PH_COLS && (!kTileOwner || active || (!in_range && (t & 1) == part));
+        if (holds_slot) {
           ok = WAIT(bar_ring_full(s), rph, ST_WAIT_RING_FULL_SM);
           if (!ok) break;
         }
         if (active) {
-          const uint32_t ts = tm_seq & 1u, tph = (tm_seq >> 1) & 1u;
+          const uint32_t tph = (ts ? tm_use[1] : tm_use[0]) & 1u;
+          if (ts) ++tm_use[1]; else ++tm_use[0];
           ok = WAIT(bar_tm_full(a, ts), tph, ST_WAIT_TMEM_FULL);
           if (!ok) break;
           ptx::tc_fence_after_sync();
@@ -564,9 +588,8 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
             }
           }
 #endif
-          ++tm_seq;
         }
-        if (PHASE == PH_COLS) {
+        if (holds_slot) {
           __syncwarp();
           if (lane == 0) ptx::mbar_arrive(bar_ring_empty(s));
         }
