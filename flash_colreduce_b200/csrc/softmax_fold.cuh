@@ -13,7 +13,11 @@ enum { RED_SUM = 0, RED_MAX = 1 };
 #ifndef FCR_POLY
 #define FCR_POLY 2
 #endif
-constexpr int kPolyOf8 = FCR_POLY;  // exponentials per 8 taken off the MUFU pipe (0, 2, 4, 6)
+// Pairs of exponentials, out of every 8 pairs (16 elements), that are evaluated by the
+// polynomial on the FMA pipe instead of MUFU: 2 = a quarter of all exponentials.
+constexpr int kPolyOf8 = FCR_POLY;
+// Spreads POLY chosen pairs evenly over each group of 8 pairs.
+__host__ __device__ constexpr bool poly_pair(int e, int poly) { return ((((e & 15) >> 1) * poly) & 7) < poly; }
 
 // ---------------------------------------------------------------- rows pass
 // One 32-column chunk of a query row: online max / sum in the base-2 domain
@@ -48,7 +52,7 @@ __device__ __forceinline__ void rows_chunk(const uint32_t* r, float scale2, int 
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
       t[u] = fmaf(x[e + u], scale2, nm);
-      if (!MASKED && ((e + u) & 7) < POLY) t[u] = ptx::ex2_poly(t[u]);
+      if (!MASKED && poly_pair(e + u, POLY)) t[u] = ptx::ex2_poly(t[u]);
       else t[u] = ptx::ex2(t[u]);
     }
     s0 += t[0]; s1 += t[1]; s2 += t[2]; s3 += t[3];
@@ -65,13 +69,13 @@ __device__ __forceinline__ void rows_chunk(const uint32_t* r, float scale2, int 
     float2 a23 = __ffma2_rn(make_float2(x[e + 2], x[e + 3]), make_float2(scale2, scale2),
                             make_float2(nm, nm));
     // kPolyOf8 of every 8 exponentials are evaluated on the FMA pipe (never in masked tiles)
-    if (!MASKED && (e & 7) < POLY) {
+    if (!MASKED && poly_pair(e, POLY)) {
       a01 = ptx::ex2_poly2(a01);
     } else {
       a01.x = ptx::ex2(a01.x);
       a01.y = ptx::ex2(a01.y);
     }
-    if (!MASKED && ((e + 2) & 7) < POLY) {
+    if (!MASKED && poly_pair(e + 2, POLY)) {
       a23 = ptx::ex2_poly2(a23);
     } else {
       a23.x = ptx::ex2(a23.x);
@@ -103,7 +107,7 @@ __device__ __forceinline__ void cols_chunk(const uint32_t* r, const float* neg_l
       float t = fmaf(__uint_as_float(r[e]), scale2, nlv[u]);
       const bool valid = !MASKED || (e >= e_lo && e < e_hi);
       if (RED == RED_SUM) {
-        float pr = (!MASKED && (e & 7) < POLY) ? ptx::ex2_poly(t) : ptx::ex2(t);
+        float pr = (!MASKED && poly_pair(e, POLY)) ? ptx::ex2_poly(t) : ptx::ex2(t);
         if (MASKED) pr = valid ? pr : 0.f;
         acc[u] += pr;
       } else {
@@ -124,13 +128,13 @@ __device__ __forceinline__ void cols_chunk(const uint32_t* r, const float* neg_l
                             make_float2(scale2, scale2), make_float2(nl.z, nl.w));
     if (RED == RED_SUM) {
       // kPolyOf8 of every 8 exponentials are evaluated on the FMA pipe (never in masked tiles)
-      if (!MASKED && (e & 7) < POLY) {
+      if (!MASKED && poly_pair(e, POLY)) {
         t01 = ptx::ex2_poly2(t01);
       } else {
         t01.x = ptx::ex2(t01.x);
         t01.y = ptx::ex2(t01.y);
       }
-      if (!MASKED && ((e + 2) & 7) < POLY) {
+      if (!MASKED && poly_pair(e + 2, POLY)) {
         t23 = ptx::ex2_poly2(t23);
       } else {
         t23.x = ptx::ex2(t23.x);
