@@ -65,7 +65,7 @@ class Plan(C.Structure):
         ("row_splits", C.c_int32), ("col_splits", C.c_int32),
         ("row_items", C.c_int32), ("col_items", C.c_int32),
         ("row_ctas", C.c_int32), ("col_ctas", C.c_int32),
-        ("head_group", C.c_int32), ("reserved0", C.c_int32),
+        ("head_group", C.c_int32), ("short_items", C.c_int32),
         ("causal_offset", C.c_int64),
         ("valid_scores", C.c_int64),
         ("off_status", C.c_int64), ("off_neg_lse", C.c_int64),

@@ -115,19 +115,17 @@ struct PassParams : PassGeom {
   int* sched_counter;  // zero at launch; hands out work items beyond the first gridDim.x
 };
 
-template <int DPAD>
+// SHORT selects the buffering for work items that stream only a few tiles: two stationary
+// stages, so that the next item's stationary tiles are fetched while this one is computed,
+// at the price of a shallower streamed ring.  Long items keep one stationary stage and a
+// deeper ring.
+template <int DPAD, bool SHORT>
 struct SmemLayout {
   static constexpr int kTileBytes = kTile * DPAD * 2;
   static constexpr int kHalves = DPAD / 64;     // 64-element (128-byte) column slabs per tile
   static constexpr int kHalfBytes = kTile * 128;
-#ifndef FCR_KS
-#define FCR_KS 1
-#endif
-#ifndef FCR_KR
-#define FCR_KR 4
-#endif
-  static constexpr int KS = FCR_KS;             // stationary stages (items in flight)
-  static constexpr int KR = (DPAD == 128) ? FCR_KR : 2 * FCR_KR;  // streamed ring stages
+  static constexpr int KS = (DPAD == 64 || SHORT) ? 2 : 1;  // stationary stages (items in flight)
+  static constexpr int KR = (DPAD == 64) ? 6 : (SHORT ? 2 : 4);  // streamed ring stages
   static constexpr int kLseBytes = kTile * 4;
   static constexpr int off_stat = 0;
   static constexpr int off_ring = off_stat + KS * kSubTiles * kTileBytes;
@@ -138,7 +136,7 @@ struct SmemLayout {
   static constexpr int KI = 4;                   // work items announced ahead of their consumers
   static constexpr int kNumBars = 2 * KS + 2 * KR + 8 + 8 + 2 * KI;
   static constexpr int off_misc = off_bars + 8 * kNumBars;
-  static constexpr int kBytes = off_misc + 16 + 4 * KI;
+  static constexpr int kBytes = off_misc + 16 + 48 * KI;  // + the ring of announced work items
   static constexpr int kDynamicBytes = kBytes;
   static_assert(kDynamicBytes <= 232448, "exceeds the 227 KB shared memory of an sm_100 CTA");
 };
@@ -216,11 +214,11 @@ __device__ __forceinline__ void store_out(void* out, int out_dtype, size_t idx, 
   }
 }
 
-template <int PHASE, int DPAD, int RED>
+template <int PHASE, int DPAD, int RED, bool SHORT>
 __global__ void __launch_bounds__(kThreads, 1)
 pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
             const __grid_constant__ CUtensorMap tmap_strm, const PassParams p) {
-  using L = SmemLayout<DPAD>;
+  using L = SmemLayout<DPAD, SHORT>;
   constexpr int KS = L::KS, KR = L::KR;
   // The 128-byte swizzle of the operand tiles needs a 1024-byte aligned base;
   // the kernel uses no static shared memory, so the dynamic window starts there.
@@ -254,7 +252,23 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
   auto bar_sched_empty = [&](uint32_t i) { return bar0 + 8u * (2 * KS + 2 * KR + 16 + KI + i); };
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + L::off_misc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::off_misc + 4);
-  volatile int* sched_item = reinterpret_cast<volatile int*>(smem + L::off_misc + 16);
+  // Announced work items, decoded once by the TMA warp (12 ints each; head -1 ends the kernel).
+  volatile int* sched_ring = reinterpret_cast<volatile int*>(smem + L::off_misc + 16);
+  auto read_item = [&](uint32_t slot) {
+    const volatile int* e = sched_ring + slot * 12;
+    Item g;
+    g.bh = e[0];
+    g.sp = e[1];
+    g.c_lo = e[2];
+    g.c_hi = e[3];
+#pragma unroll
+    for (int a = 0; a < kSubTiles; ++a) {
+      g.r0[a] = e[4 + 3 * a];
+      g.t_lo[a] = e[5 + 3 * a];
+      g.t_hi[a] = e[6 + 3 * a];
+    }
+    return g;
+  };
 
   const int warp = (int)(threadIdx.x >> 5);
   const int lane = (int)(threadIdx.x & 31);
@@ -315,15 +329,29 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
       ok = WAIT(bar_sched_empty(si), sph ^ 1u, ST_WAIT_SCHED_EMPTY);
       if (!ok) break;
       const bool last = item >= p.n_items;
+      Item g;
+      g.bh = -1;
+      if (!last) g = decode_item<PHASE == PH_COLS>(p, item);
       int next_item = 0;
       if (lane == 0) {
-        sched_item[si] = last ? -1 : item;
+        volatile int* e = sched_ring + si * 12;
+        e[0] = g.bh;
+        if (!last) {
+          e[1] = g.sp;
+          e[2] = g.c_lo;
+          e[3] = g.c_hi;
+#pragma unroll
+          for (int a = 0; a < kSubTiles; ++a) {
+            e[4 + 3 * a] = g.r0[a];
+            e[5 + 3 * a] = g.t_lo[a];
+            e[6 + 3 * a] = g.t_hi[a];
+          }
+        }
         ptx::mbar_arrive(bar_sched_full(si));
         if (!last) next_item = (int)gridDim.x + atomicAdd(p.sched_counter, 1);
       }
       __syncwarp();
       if (last) break;
-      const Item g = decode_item<PHASE == PH_COLS>(p, item);
       const int b = g.bh / p.H, h = g.bh - b * p.H;
       const uint32_t ks = item_seq % KS, kph = (item_seq / KS) & 1u;
       ok = WAIT(bar_stat_empty(ks), kph ^ 1u, ST_WAIT_STAT_EMPTY);
@@ -381,11 +409,10 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
       const uint32_t si = item_seq % KI, sph = (item_seq / KI) & 1u;
       ok = WAIT(bar_sched_full(si), sph, ST_WAIT_SCHED_FULL);
       if (!ok) break;
-      const int item = sched_item[si];
+      const Item g = read_item(si);
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(bar_sched_empty(si));
-      if (item < 0) break;
-      const Item g = decode_item<PHASE == PH_COLS>(p, item);
+      if (g.bh < 0) break;
       const uint32_t ks = item_seq % KS, kph = (item_seq / KS) & 1u;
       ok = WAIT(bar_stat_full(ks), kph, ST_WAIT_STAT_FULL);
       if (!ok) break;
@@ -456,11 +483,10 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
       const uint32_t si = item_seq % KI, sph = (item_seq / KI) & 1u;
       ok = WAIT(bar_sched_full(si), sph, ST_WAIT_SCHED_FULL_SM);
       if (!ok) break;
-      const int item = sched_item[si];
+      const Item g = read_item(si);
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(bar_sched_empty(si));
-      if (item < 0) break;
-      const Item g = decode_item<PHASE == PH_COLS>(p, item);
+      if (g.bh < 0) break;
       const int mine = g.r0[a] + tid_wg;  // query row (rows pass) or key column (columns pass)
       float m_run = -INFINITY, l_run = 0.f;
       float acc[4];
@@ -862,11 +888,11 @@ static uint32_t instr_desc(int dtype, bool negate_a) {
          ((uint32_t)(kTile >> 3) << 17) | ((uint32_t)(kTile >> 4) << 24);
 }
 
-template <int PHASE, int DPAD, int RED>
+template <int PHASE, int DPAD, int RED, bool SHORT>
 static int launch_pass(const CUtensorMap& stat, const CUtensorMap& strm, const PassParams& pp,
                        int ctas, cudaStream_t stream) {
-  auto kern = pass_kernel<PHASE, DPAD, RED>;
-  constexpr int smem = SmemLayout<DPAD>::kDynamicBytes;
+  auto kern = pass_kernel<PHASE, DPAD, RED, SHORT>;
+  constexpr int smem = SmemLayout<DPAD, SHORT>::kDynamicBytes;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute");
   kern<<<ctas, kThreads, smem, stream>>>(stat, strm, pp);
@@ -876,10 +902,12 @@ static int launch_pass(const CUtensorMap& stat, const CUtensorMap& strm, const P
 }
 
 template <int PHASE, int RED>
-static int launch_pass_d(int d_pad, const CUtensorMap& stat, const CUtensorMap& strm,
-                         const PassParams& pp, int ctas, cudaStream_t stream) {
-  if (d_pad == 64) return launch_pass<PHASE, 64, RED>(stat, strm, pp, ctas, stream);
-  return launch_pass<PHASE, 128, RED>(stat, strm, pp, ctas, stream);
+static int launch_pass_d(int d_pad, bool short_items, const CUtensorMap& stat,
+                         const CUtensorMap& strm, const PassParams& pp, int ctas,
+                         cudaStream_t stream) {
+  if (d_pad == 64) return launch_pass<PHASE, 64, RED, false>(stat, strm, pp, ctas, stream);
+  if (short_items) return launch_pass<PHASE, 128, RED, true>(stat, strm, pp, ctas, stream);
+  return launch_pass<PHASE, 128, RED, false>(stat, strm, pp, ctas, stream);
 }
 
 static int check_workspace(const fcr_plan& pl, const void* ws, size_t ws_bytes) {
@@ -998,7 +1026,8 @@ int fcr_colreduce(const fcr_problem* problem, const void* q, const void* k, void
   trace_mark(0, stream);
   PassParams pp;
   fill_common(pp, pr, pl, ws, false);
-  rc = launch_pass_d<PH_ROWS, RED_SUM>(pl.d_pad, map_q, map_k, pp, pl.row_ctas, stream);
+  rc = launch_pass_d<PH_ROWS, RED_SUM>(pl.d_pad, (pl.short_items & 1) != 0, map_q, map_k, pp,
+                                       pl.row_ctas, stream);
   if (rc != FCR_OK) return rc;
   if (pl.row_splits > 1) {
     const size_t per_split = (size_t)pp.BH * pl.m_pad;
@@ -1017,9 +1046,11 @@ int fcr_colreduce(const fcr_problem* problem, const void* q, const void* k, void
   fill_mean(pp, pr.reduction, pr.is_causal, pr.mean_M > 0 ? pr.mean_M : pr.M,
             pr.mean_N > 0 ? pr.mean_N : pr.N);
   if (pr.reduction == FCR_MAX)
-    rc = launch_pass_d<PH_COLS, RED_MAX>(pl.d_pad, map_k, map_q, pp, pl.col_ctas, stream);
+    rc = launch_pass_d<PH_COLS, RED_MAX>(pl.d_pad, (pl.short_items & 2) != 0, map_k, map_q, pp,
+                                         pl.col_ctas, stream);
   else
-    rc = launch_pass_d<PH_COLS, RED_SUM>(pl.d_pad, map_k, map_q, pp, pl.col_ctas, stream);
+    rc = launch_pass_d<PH_COLS, RED_SUM>(pl.d_pad, (pl.short_items & 2) != 0, map_k, map_q, pp,
+                                         pl.col_ctas, stream);
   if (rc != FCR_OK) return rc;
   if (pl.col_splits > 1) {
     const size_t per_split = (size_t)pp.BH * pl.n_pad;
@@ -1122,7 +1153,7 @@ int fcr_debug_scores(const fcr_problem* problem, const void* q, const void* k, f
   rc = device_sm_count(&sms);
   if (rc != FCR_OK) return rc;
   const int ctas = std::min(pp.n_items, sms);
-  return launch_pass_d<PH_DUMP, RED_SUM>(pl.d_pad, map_q, map_k, pp, ctas, stream);
+  return launch_pass_d<PH_DUMP, RED_SUM>(pl.d_pad, false, map_q, map_k, pp, ctas, stream);
 }
 
 // ----------------------------------------------------------------------

@@ -220,6 +220,9 @@ inline int plan_problem(const fcr_problem& p, int num_sms, fcr_plan& pl, std::st
   pl.head_group = !causal ? 1
                           : (int32_t)std::max<int64_t>(
                                 1, std::min<int64_t>(std::min<int64_t>(BH, 16), (40LL << 20) / head_bytes));
+  // Items that stream at most 8 tiles get the double-buffered stationary stage.
+  pl.short_items = (ceil_div64(row_len, pl.row_splits) <= 8 ? 1 : 0) |
+                   (ceil_div64(col_len, pl.col_splits) <= 8 ? 2 : 0);
   pl.row_ctas = (int32_t)std::min<int64_t>(row_items, num_sms);
   pl.col_ctas = (int32_t)std::min<int64_t>(col_items, num_sms);
 

@@ -87,7 +87,7 @@ typedef struct fcr_plan {
   int32_t row_items, col_items; /* work items per phase = B*H*blocks*splits */
   int32_t row_ctas, col_ctas;   /* persistent CTAs launched per phase */
   int32_t head_group;       /* heads whose work items are interleaved so that they share the L2 cache */
-  int32_t reserved0;
+  int32_t short_items;      /* bit 0 / 1: the rows / columns pass uses the buffering for items of few tiles */
   int64_t causal_offset;    /* resolved offset */
   int64_t valid_scores;     /* B*H*sum_i valid(i): the unit the throughput metric counts */
   /* workspace layout, byte offsets from the workspace base */
