@@ -261,6 +261,7 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
     g.sp = e[1];
     g.c_lo = e[2];
     g.c_hi = e[3];
+    g.par = e[10];
 #pragma unroll
     for (int a = 0; a < kSubTiles; ++a) {
       g.r0[a] = e[4 + 3 * a];
@@ -319,43 +320,18 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
     // ------------------------------------------------------------ TMA warp
     PROF_DECL();
     // Work items are handed out dynamically: the first is the CTA's own index,
-    // later ones come from a global counter.  Each is announced to the other
-    // warps through a small ring in shared memory; -1 ends the kernel.
+    // later ones come from a global counter (fetched one item early, so that the
+    // atomic's latency is hidden).  Each item is decoded here once and announced
+    // to the other warps through a small ring in shared memory; head -1 ends the
+    // kernel.  With two stationary stages the stationary tiles of item i+1 are
+    // requested before the streamed tiles of item i, i.e. a whole item ahead.
+    constexpr bool kAhead = KS >= 2;
     uint32_t ring_seq = 0, item_seq = 0;
     bool ok = true;
-    int item = (int)blockIdx.x;
-    for (;; ++item_seq) {
-      const uint32_t si = item_seq % KI, sph = (item_seq / KI) & 1u;
-      ok = WAIT(bar_sched_empty(si), sph ^ 1u, ST_WAIT_SCHED_EMPTY);
-      if (!ok) break;
-      const bool last = item >= p.n_items;
-      Item g;
-      g.bh = -1;
-      if (!last) g = decode_item<PHASE == PH_COLS>(p, item);
-      int next_item = 0;
-      if (lane == 0) {
-        volatile int* e = sched_ring + si * 12;
-        e[0] = g.bh;
-        if (!last) {
-          e[1] = g.sp;
-          e[2] = g.c_lo;
-          e[3] = g.c_hi;
-#pragma unroll
-          for (int a = 0; a < kSubTiles; ++a) {
-            e[4 + 3 * a] = g.r0[a];
-            e[5 + 3 * a] = g.t_lo[a];
-            e[6 + 3 * a] = g.t_hi[a];
-          }
-        }
-        ptx::mbar_arrive(bar_sched_full(si));
-        if (!last) next_item = (int)gridDim.x + atomicAdd(p.sched_counter, 1);
-      }
-      __syncwarp();
-      if (last) break;
+    auto load_stationary = [&](const Item& g, uint32_t seq) {
       const int b = g.bh / p.H, h = g.bh - b * p.H;
-      const uint32_t ks = item_seq % KS, kph = (item_seq / KS) & 1u;
-      ok = WAIT(bar_stat_empty(ks), kph ^ 1u, ST_WAIT_STAT_EMPTY);
-      if (!ok) break;
+      const uint32_t ks = seq % KS, kph = (seq / KS) & 1u;
+      if (!WAIT(bar_stat_empty(ks), kph ^ 1u, ST_WAIT_STAT_EMPTY)) return false;
       if (lane == 0) {
         ptx::mbar_arrive_expect_tx(bar_stat_full(ks), kSubTiles * L::kTileBytes);
 #pragma unroll
@@ -366,6 +342,56 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
                              &tmap_stat, bar_stat_full(ks), hf * 64, g.r0[a], h, b);
       }
       __syncwarp();
+      return true;
+    };
+    auto fetch_index = [&]() {  // next work-item index from the global counter (all lanes get it)
+      int v = 0;
+      if (lane == 0) v = (int)gridDim.x + atomicAdd(p.sched_counter, 1);
+      return __shfl_sync(0xffffffffu, v, 0);
+    };
+    int item = (int)blockIdx.x;
+    int item_next = fetch_index();
+    Item g;
+    g.bh = -1;
+    if (item < p.n_items) g = decode_item<PHASE == PH_COLS>(p, item);
+    if (kAhead && g.bh >= 0) ok = load_stationary(g, 0);
+    for (; ok; ++item_seq) {
+      const uint32_t si = item_seq % KI, sph = (item_seq / KI) & 1u;
+      ok = WAIT(bar_sched_empty(si), sph ^ 1u, ST_WAIT_SCHED_EMPTY);
+      if (!ok) break;
+      const bool last = g.bh < 0;
+      if (lane == 0) {
+        volatile int* e = sched_ring + si * 12;
+        e[0] = g.bh;
+        if (!last) {
+          e[1] = g.sp;
+          e[2] = g.c_lo;
+          e[3] = g.c_hi;
+          e[10] = g.par;
+#pragma unroll
+          for (int a = 0; a < kSubTiles; ++a) {
+            e[4 + 3 * a] = g.r0[a];
+            e[5 + 3 * a] = g.t_lo[a];
+            e[6 + 3 * a] = g.t_hi[a];
+          }
+        }
+        ptx::mbar_arrive(bar_sched_full(si));
+      }
+      __syncwarp();
+      if (last) break;
+      // the item after this one, and the index of the one after that
+      Item g_next;
+      g_next.bh = -1;
+      if (item_next < p.n_items) g_next = decode_item<PHASE == PH_COLS>(p, item_next);
+      item = item_next;
+      item_next = (item < p.n_items) ? fetch_index() : item;
+      if (kAhead) {
+        if (g_next.bh >= 0) ok = load_stationary(g_next, item_seq + 1);
+      } else {
+        ok = load_stationary(g, item_seq);
+      }
+      if (!ok) break;
+      const int b = g.bh / p.H, h = g.bh - b * p.H;
       for (int t = g.c_lo; t < g.c_hi; ++t, ++ring_seq) {
         const uint32_t s = ring_seq % KR, ph = (ring_seq / KR) & 1u;
         ok = WAIT(bar_ring_empty(s), ph ^ 1u, ST_WAIT_RING_EMPTY);
@@ -384,8 +410,7 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
         }
         __syncwarp();
       }
-      if (!ok) break;
-      item = __shfl_sync(0xffffffffu, next_item, 0);
+      g = g_next;
     }
 #ifdef FCR_PROFILE
     prof_acc[0] = clock64() - prof_t0;
@@ -399,8 +424,8 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
     // handshakes overlap the other's MMAs.
     PROF_DECL();
     const int a = warp - kMmaWarp;
-    // Accumulator buffer of a tile = its index within the work item, mod 2 (so that the
-    // warpgroup that folds it does not depend on which items this CTA happened to get);
+    // Accumulator buffer of a tile = (its index within the work item + the item's parity) mod 2,
+    // so that the warpgroup that folds it does not depend on which items this CTA happened to get;
     // tm_use[b] counts the uses of buffer b and gives its barrier phase.
     uint32_t ring_seq = 0, item_seq = 0;
     uint32_t tm_use[2] = {0, 0};
@@ -423,7 +448,7 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
         ok = WAIT(bar_ring_full(s), ph, ST_WAIT_RING_FULL);
         if (!ok) break;
         if (t >= g.t_lo[a] && t < g.t_hi[a]) {
-          const uint32_t ts = (uint32_t)(t - g.t_lo[a]) & 1u;
+          const uint32_t ts = (uint32_t)(t - g.t_lo[a] + g.par) & 1u;
           const uint32_t tph = (ts ? tm_use[1] : tm_use[0]) & 1u;
           ok = WAIT(bar_tm_empty(a, ts), tph ^ 1u, ST_WAIT_TMEM_EMPTY);
           if (!ok) break;
@@ -511,7 +536,10 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
       uint32_t rs = ring_base;
       for (int t = g.c_lo; ok && t < g.c_hi; ++t, ++rs) {
         const bool in_range = (t >= g.t_lo[a]) && (t < g.t_hi[a]);
-        const uint32_t ts = (uint32_t)(t - g.t_lo[a]) & 1u;  // accumulator buffer of this tile
+        // accumulator buffer of this tile: alternates within the item, starting from the
+        // parity of the item's index (a property of the item, so the result does not depend
+        // on which CTA runs it; short items then spread over both warpgroups)
+        const uint32_t ts = (uint32_t)(t - g.t_lo[a] + g.par) & 1u;
         // with tile ownership a warpgroup folds every other tile of its sub-tile
         const bool active = in_range && (!kTileOwner || (int)ts == part);
         const uint32_t s = rs % KR, rph = (rs / KR) & 1u;

@@ -41,6 +41,7 @@ struct PassGeom {
 // stationary sub-tile a; the item streams tiles [c_lo, c_hi).
 struct Item {
   int bh, sp;
+  int par;  // parity of the item's index: which accumulator buffer its first tile uses
   int r0[kSubTiles];
   int t_lo[kSubTiles], t_hi[kSubTiles];
   int c_lo, c_hi;
@@ -73,6 +74,7 @@ FCR_HD Item decode_item(const PassGeom& p, int item) {
   const int o = in_grp / heads_here;
   g.bh = grp * p.head_group + (in_grp - o * heads_here);
   g.sp = sp;
+  g.par = item & 1;
   const int sb = p.sb_reverse ? (p.n_sb - 1 - o) : o;
   int lo = 0x7fffffff, hi = 0;
   int tb[kSubTiles], te[kSubTiles];
