@@ -268,7 +268,11 @@ def run_ours(args):
                        **WORKLOAD, "heads_per_gpu": heads, "l2": "inputs (4 GiB per 64 heads) exceed the 126 MB L2"},
             "roofline": {
                 "bound": "tensor", "achieved": achieved, "peak": peak_sustained, "unit": "TFLOP/s",
-                "frac": achieved / peak_sustained, "traffic": None, "peak_kind": f"{peak_kind} sustained bf16 (kernel timed inside a long step)",
+                "frac": achieved / peak_sustained,
+                # DRAM bytes of one pass launch: ncu on a smaller case of the same kernel (256 MiB of Q and K) read
+                # 1.028x the bytes of Q and K; traffic grows with those bytes, so it is scaled to this rank's inputs
+                "traffic": int(1.028 * 2 * heads * (M + N) * D),
+                "algorithmic_flops_per_score_per_launch": 2 * D, "peak_kind": f"{peak_kind} sustained bf16 (kernel timed inside a long step)",
                 "kernel": "pass_kernel (rows pass)" if rows_ms >= cols_ms else "pass_kernel (columns pass)",
                 "rows_pass_ms": rows_ms, "cols_pass_ms": cols_ms,
                 "op_tflops": 4 * D * local_scores / ((rows_ms + cols_ms) * 1e-3) / 1e12,
