@@ -71,8 +71,8 @@ constexpr int kSpan = kTileOwner ? kTile : kTile / kColSplit;  // columns of a t
 #ifndef FCR_CHUNK_COLS
 #define FCR_CHUNK_COLS 32
 #endif
-// accumulator columns per tensor-memory load: one load per tile in the rows pass (one
-// running-max update per 64 keys), two in the columns pass (the lse operands cost registers)
+// accumulator columns per tensor-memory load: 64 in the rows pass (one running-max update
+// per 64 keys), 32 in the columns pass (the lse operands cost registers)
 constexpr int kChunkRows = FCR_CHUNK_ROWS;
 constexpr int kChunkCols = FCR_CHUNK_COLS;
 static_assert(kSpan % kChunkRows == 0 && kChunkRows % 32 == 0 && kSpan % kChunkCols == 0 &&
@@ -588,7 +588,6 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
                 cols_chunk<RED, false, kChunk>(r, lse_s + kChunk * c, p.scale2, 0, kChunk, acc);
             }
           };
-#ifndef FCR_DOUBLEBUF
           // one chunk at a time: the other warps of the scheduler cover the load latency
 #pragma unroll
           for (int c = 0; c < kSpan / kChunk; ++c) {
@@ -609,39 +608,6 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
               PROF_ADD(34);
             }
           }
-#else
-          uint32_t rb[kChunk];
-          // chunk c+1 is in flight from tensor memory while chunk c is folded
-          {
-            PROF_T0();
-            ptx::tmem_ld<kChunk>(taddr, ra);
-            ptx::tmem_ld_wait<kChunk>(ra);
-            PROF_ADD(33);
-          }
-#pragma unroll
-          for (int c = 0; c < kSpan / kChunk; ++c) {
-            uint32_t* cur = (c & 1) ? rb : ra;
-            uint32_t* nxt = (c & 1) ? ra : rb;
-            if (c + 1 < kSpan / kChunk) {
-              ptx::tmem_ld<kChunk>(taddr + (c + 1) * kChunk, nxt);
-            } else {
-              // every lane holds the rest of its span: hand the accumulator back
-              ptx::tc_fence_before_sync();
-              __syncwarp();
-              if (lane == 0) ptx::mbar_arrive(bar_tm_empty(a, ts));
-            }
-            {
-              PROF_T0();
-              consume(cur, c);
-              PROF_ADD(34);
-            }
-            if (c + 1 < kSpan / kChunk) {
-              PROF_T0();
-              ptx::tmem_ld_wait<kChunk>(nxt);
-              PROF_ADD(35);
-            }
-          }
-#endif
         }
         if (holds_slot) {
           __syncwarp();

@@ -193,19 +193,6 @@ __device__ __forceinline__ float2 ex2_poly2(float2 x) {
   return r;
 }
 
-// Scalar form of ex2_poly2.
-__device__ __forceinline__ float ex2_poly(float x) {
-  const float kMagic = 12582912.0f;
-  x = fmaxf(x, -126.f);
-  const float t = x + kMagic;
-  const float f = x - (t - kMagic);
-  float p = fmaf(f, 0.009570101753f, 0.05591786031f);
-  p = fmaf(p, f, 0.2402474483f);
-  p = fmaf(p, f, 0.6931218147f);
-  p = fmaf(p, f, 0.9999992614f);
-  return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
-}
-
 // ------------------------------------------------- tcgen05 descriptor helpers
 // Shared-memory matrix descriptor for a K-major operand tile stored as rows of
 // 128 bytes with the 128-byte swizzle (what a TMA box of 64 fp16 x rows with

@@ -44,23 +44,6 @@ __device__ __forceinline__ void rows_chunk(const uint32_t* r, float scale2, int 
   const float m_safe = (m_new == -INFINITY) ? 0.f : m_new;  // row sees nothing yet
   const float alpha = ptx::ex2(m_run - m_safe);
   const float nm = -m_safe;
-#ifdef FCR_SCALAR
-  float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
-#pragma unroll
-  for (int e = 0; e < W; e += 4) {
-    float t[4];
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      t[u] = fmaf(x[e + u], scale2, nm);
-      if (!MASKED && poly_pair(e + u, POLY)) t[u] = ptx::ex2_poly(t[u]);
-      else t[u] = ptx::ex2(t[u]);
-    }
-    s0 += t[0]; s1 += t[1]; s2 += t[2]; s3 += t[3];
-  }
-  l_run = fmaf(l_run, alpha, (s0 + s1) + (s2 + s3));
-  m_run = m_new;
-  return;
-#endif
   float2 s01 = make_float2(0.f, 0.f), s23 = make_float2(0.f, 0.f);
 #pragma unroll
   for (int e = 0; e < W; e += 4) {
@@ -96,28 +79,6 @@ __device__ __forceinline__ void rows_chunk(const uint32_t* r, float scale2, int 
 template <int RED, bool MASKED, int W, int POLY = kPolyOf8>
 __device__ __forceinline__ void cols_chunk(const uint32_t* r, const float* neg_lse,
                                            float scale2, int e_lo, int e_hi, float (&acc)[4]) {
-#ifdef FCR_SCALAR
-#pragma unroll
-  for (int q = 0; q < W / 4; ++q) {
-    const float4 nl = reinterpret_cast<const float4*>(neg_lse)[q];
-    const float nlv[4] = {nl.x, nl.y, nl.z, nl.w};
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const int e = q * 4 + u;
-      float t = fmaf(__uint_as_float(r[e]), scale2, nlv[u]);
-      const bool valid = !MASKED || (e >= e_lo && e < e_hi);
-      if (RED == RED_SUM) {
-        float pr = (!MASKED && poly_pair(e, POLY)) ? ptx::ex2_poly(t) : ptx::ex2(t);
-        if (MASKED) pr = valid ? pr : 0.f;
-        acc[u] += pr;
-      } else {
-        if (MASKED) t = valid ? t : -INFINITY;
-        acc[u] = fmaxf(acc[u], t);
-      }
-    }
-  }
-  return;
-#endif
 #pragma unroll
   for (int q = 0; q < W / 4; ++q) {
     const float4 nl = reinterpret_cast<const float4*>(neg_lse)[q];
