@@ -34,6 +34,7 @@
 #include <string.h>
 
 #include <array>
+#include <atomic>
 #include <mutex>
 #include <string>
 #include <vector>
@@ -887,8 +888,17 @@ static int launch_pass(const CUtensorMap& stat, const CUtensorMap& strm, const P
                        int ctas, cudaStream_t stream) {
   auto kern = pass_kernel<PHASE, DPAD, RED, SHORT>;
   constexpr int smem = SmemLayout<DPAD, SHORT>::kDynamicBytes;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-  if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute");
+  // the shared-memory opt-in is per kernel and device: do it once for each
+  static std::atomic<unsigned long long> opted_in{0};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+  const unsigned long long bit = 1ULL << (dev & 63);
+  if (!(opted_in.load(std::memory_order_acquire) & bit)) {
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute");
+    opted_in.fetch_or(bit, std::memory_order_release);
+  }
   kern<<<ctas, kThreads, smem, stream>>>(stat, strm, pp);
   e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "pass kernel launch");

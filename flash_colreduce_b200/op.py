@@ -44,17 +44,34 @@ def _tma_ready(x: torch.Tensor) -> torch.Tensor:
     return x if ok else x.contiguous()
 
 
+_PLAN_CACHE: dict = {}
+
+
+def _problem_and_workspace_bytes(key_tuple, device):
+    """Problem struct and workspace size for a call signature (cached: planning is pure host work)."""
+    hit = _PLAN_CACHE.get(key_tuple)
+    if hit is None:
+        (b, h, m, n, d, qs, ks, dt, red, causal, scale, off, mean_m, mean_n, _dev) = key_tuple
+        prob = nat.make_problem(b, h, m, n, d, qs, ks, dt, red, causal, scale, off, mean_m, mean_n)
+        with torch.cuda.device(device):
+            pl = nat.plan(prob, 0)
+        if len(_PLAN_CACHE) > 4096:
+            _PLAN_CACHE.clear()
+        hit = _PLAN_CACHE[key_tuple] = (prob, int(pl.workspace_bytes))
+    return hit
+
+
 def _launch(query, key, out, out_code, reduction_code, is_causal, scale, causal_offset, mean_M, mean_N):
     b, h, m, _ = query.shape
     n = key.shape[2]
     q = _tma_ready(query)
     k = _tma_ready(key)
     d = q.shape[-1]
-    prob = nat.make_problem(b, h, m, n, d, q.stride(), k.stride(), _DTYPE_CODES[q.dtype],
-                            reduction_code, is_causal, scale, causal_offset, mean_M, mean_N)
+    prob, ws_bytes = _problem_and_workspace_bytes(
+        (b, h, m, n, d, tuple(q.stride()), tuple(k.stride()), _DTYPE_CODES[q.dtype], reduction_code, bool(is_causal),
+         float(scale), int(causal_offset), int(mean_M), int(mean_N), q.device.index), q.device)
     with torch.cuda.device(q.device):
-        pl = nat.plan(prob, 0)
-        ws = torch.empty(int(pl.workspace_bytes), dtype=torch.uint8, device=q.device)
+        ws = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device)
         stream = torch.cuda.current_stream(q.device).cuda_stream
         rc = nat.lib.fcr_colreduce(C.byref(prob), q.data_ptr(), k.data_ptr(), out.data_ptr(), out_code,
                                    ws.data_ptr(), ws.numel(), stream)
