@@ -168,6 +168,34 @@ def test_more_queries_than_keys_and_edge_shapes(m, n):
             assert_parity(_f32(q.to(dev), k.to(dev), red, causal), oracle_colreduce(q, k, red, causal), red)
 
 
+@pytest.mark.parametrize("b,h,m,n,d", [(1, 1, 1, 1, 8), (3, 5, 1, 7, 8), (2, 2, 7, 1, 24), (16, 64, 2, 3, 16),
+                                       (1, 2, 129, 255, 120), (1, 1, 257, 129, 104), (1, 3, 640, 384, 128)])
+def test_degenerate_and_odd_head_dims(b, h, m, n, d):
+    dev = _dev()
+    q, k = _rand((b, h, m, d), 30), _rand((b, h, n, d), 31)
+    for red in ("sum", "mean", "max"):
+        for causal in (False, True):
+            assert_parity(_f32(q.to(dev), k.to(dev), red, causal), oracle_colreduce(q, k, red, causal), red)
+
+
+def test_zero_scale_gives_uniform_rows():
+    dev = _dev()
+    q, k = _rand((1, 2, 100, 64), 32), _rand((1, 2, 300, 64), 33)
+    got = _f32(q.to(dev), k.to(dev), "sum", False, 0.0)
+    torch.testing.assert_close(got.cpu(), torch.full((1, 2, 300), 100.0 / 300.0), rtol=1e-5, atol=1e-6)
+    assert_parity(_f32(q.to(dev), k.to(dev), "mean", True, 0.0), oracle_colreduce(q, k, "mean", True, 0.0), "mean")
+
+
+def test_many_heads_and_batch_strides():
+    """More work items than any one CTA sees, and a batch taken out of a larger tensor."""
+    dev = _dev()
+    q, k = _rand((6, 40, 130, 64), 34), _rand((6, 40, 200, 64), 35)
+    qd, kd = q.to(dev), k.to(dev)
+    assert_parity(_f32(qd, kd, "sum", True), oracle_colreduce(q, k, "sum", True), "sum")
+    assert_parity(_f32(qd[1:5:2, 3:33], kd[1:5:2, 3:33], "mean", True),
+                  oracle_colreduce(q[1:5:2, 3:33], k[1:5:2, 3:33], "mean", True), "mean")
+
+
 @pytest.mark.parametrize("scale", [0.3, -0.2, 1.5])
 def test_user_scale(scale):
     dev = _dev()
