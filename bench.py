@@ -263,7 +263,7 @@ def run_ours(args):
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "fp16 operands, fp32 accumulate", "data": "synthetic",
+            "vs_baseline": None, "dtype": "fp16", "data": "synthetic",
             "config": {"workload": "long-context B=1 H=64 M=N=131072 d=128 fp16 causal sum, heads partitioned over GPUs",
                        **WORKLOAD, "heads_per_gpu": heads, "l2": "inputs (4 GiB per 64 heads) exceed the 126 MB L2"},
             "roofline": {

@@ -13,6 +13,19 @@ for p in (ROOT, os.path.join(ROOT, "tests")):
 GOLDEN_PATH = os.path.join(ROOT, "tests", "golden", "naive_golden.npz")
 
 
+def _ensure_library_built():
+    """Builds the sm_100a library in-tree when it is missing or older than its sources (nvcc cross-compiles)."""
+    import importlib.util
+
+    spec = importlib.util.spec_from_file_location("_fcr_build", os.path.join(ROOT, "flash_colreduce_b200", "build.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    mod.build()
+
+
+_ensure_library_built()
+
+
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (B200, sm_100a)")
 
