@@ -22,7 +22,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 
 # (name, B, H, M, N, D, seed, scale)
 INPUT_SETS = [
-    ("c1", 2, 4, 256, 256, 64, 0, None),           # BASELINE config 0
+    ("c1", 2, 4, 256, 256, 64, 0, None),           # the reference's CPU-runnable benchmark configuration
     ("sq128_d16", 1, 1, 128, 128, 16, 1, None),    # the reference test matrix, tests/test_correctness.py:8-13
     ("sq131_d72", 1, 1, 131, 131, 72, 2, None),
     ("dec128_d72", 1, 1, 128, 1024, 72, 3, None),
@@ -35,7 +35,9 @@ REDUCTIONS = ("sum", "mean", "max")
 
 
 def main() -> None:
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_golden.py /path/to/flash-colreduce")
+    ref_root = sys.argv[1]
     sys.path.insert(0, ref_root)
     from flash_colreduce.naive import naive_colreduce  # the reference, unmodified
 
