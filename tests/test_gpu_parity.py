@@ -260,3 +260,27 @@ def test_runs_on_the_current_stream_without_sync():
         other = flash_colreduce(q, k, "sum")
     s.synchronize()
     assert torch.equal(base, other)
+
+
+def test_capturable_in_a_cuda_graph():
+    """The whole call (memset + kernels, no host sync) can be captured once and replayed."""
+    from flash_colreduce_b200 import flash_colreduce
+
+    dev = _dev()
+    q, k = _rand((2, 4, 300, 64), 40).to(dev), _rand((2, 4, 700, 64), 41).to(dev)
+    os.environ["FCR_DEBUG_SYNC"] = "0"  # the status read-back synchronises, which a capture forbids
+    try:
+        eager = flash_colreduce(q, k, "mean", is_causal=True)  # also performs the one-time kernel set-up
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            captured = flash_colreduce(q, k, "mean", is_causal=True)
+        q2 = _rand((2, 4, 300, 64), 42).to(dev)
+        q.copy_(q2)  # new inputs in the captured buffers
+        graph.replay()
+        torch.cuda.synchronize()
+    finally:
+        os.environ["FCR_DEBUG_SYNC"] = "1"
+    want = flash_colreduce(q, k, "mean", is_causal=True)
+    assert torch.equal(captured, want)
+    assert not torch.equal(captured, eager)
