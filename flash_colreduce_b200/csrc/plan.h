@@ -133,11 +133,23 @@ inline int64_t valid_keys(int64_t i, int64_t N, bool causal, int64_t off) {
 }
 
 inline int choose_splits(int64_t base_items, int64_t max_len_tiles, int num_sms) {
-  // Split the streamed range until the grid covers the SMs about twice, never
-  // below one tile per chunk.
-  int s = 1;
-  while (base_items * s < 2LL * num_sms && 2LL * s <= max_len_tiles && s < 64) s *= 2;
-  return s;
+  // Splitting the streamed range of an item S ways shortens the critical path of a small
+  // problem (more CTAs work in parallel) but costs a combine kernel and per-item set-up.
+  // Cost model in units of one streamed tile step: every item pays 2 steps of set-up,
+  // the combine launch about 3; items run in waves of num_sms.  Large problems (at least
+  // one full wave without splitting) never split.
+  int best = 1;
+  int64_t best_cost = -1;
+  for (int s = 1; s <= 64 && s <= max_len_tiles; s *= 2) {
+    const int64_t waves = ceil_div64(base_items * s, num_sms);
+    const int64_t cost = waves * (ceil_div64(max_len_tiles, s) + 2) + (s > 1 ? 3 : 0);
+    if (best_cost < 0 || cost < best_cost) {
+      best_cost = cost;
+      best = s;
+    }
+    if (base_items * s >= num_sms) break;  // the grid is full: more splits only add overhead
+  }
+  return best;
 }
 
 inline int plan_problem(const fcr_problem& p, int num_sms, fcr_plan& pl, std::string& err) {
