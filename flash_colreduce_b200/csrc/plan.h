@@ -227,13 +227,13 @@ inline int plan_problem(const fcr_problem& p, int num_sms, fcr_plan& pl, std::st
   pl.row_items = (int32_t)row_items;
   pl.col_items = (int32_t)col_items;
   // With the causal mask the items of a head shrink towards its end: interleave the
-  // heads whose Q and K (fp16) fit a 40 MiB share of the L2 cache together (16 at most),
+  // heads whose Q and K (fp16) total at most 128 MiB (32 heads at most; measured flat from 16 to 32),
   // so that the tail of the grid is made of the lightest items of many heads.  Without
   // the mask all items weigh the same and one head at a time keeps the CTAs in step.
   const int64_t head_bytes = ((int64_t)p.M + p.N) * pl.d_pad * 2;
   pl.head_group = !causal ? 1
                           : (int32_t)std::max<int64_t>(
-                                1, std::min<int64_t>(std::min<int64_t>(BH, 16), (40LL << 20) / head_bytes));
+                                1, std::min<int64_t>(std::min<int64_t>(BH, 32), (128LL << 20) / head_bytes));
   // Items that stream at most 8 tiles get the double-buffered stationary stage.
   pl.short_items = (ceil_div64(row_len, pl.row_splits) <= 8 ? 1 : 0) |
                    (ceil_div64(col_len, pl.col_splits) <= 8 ? 2 : 0);
