@@ -277,6 +277,8 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
 #ifdef FCR_PROFILE
   if (threadIdx.x < 40) g_prof[threadIdx.x] = 0;
   const long long prof_t0 = clock64();
+  unsigned long long prof_g0;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(prof_g0));
 #endif
 
   if (threadIdx.x == 0) {
@@ -705,6 +707,16 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
   if (threadIdx.x < 40)
     atomicAdd(reinterpret_cast<unsigned long long*>(p.status + 16) + threadIdx.x +
                   (PHASE == PH_COLS ? 40 : 0), g_prof[threadIdx.x]);
+  if (threadIdx.x == 0) {
+    // wall-clock span of the CTAs: earliest start, latest end, sum of lifetimes (ns)
+    unsigned long long g1;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g1));
+    unsigned long long* w = reinterpret_cast<unsigned long long*>(p.status + 16) + 80 + (PHASE == PH_COLS ? 4 : 0);
+    atomicMin(w + 0, prof_g0);
+    atomicMax(w + 1, g1);
+    atomicAdd(w + 2, g1 - prof_g0);
+    atomicMax(w + 3, g1 - prof_g0);
+  }
 #endif
 }
 
@@ -1025,6 +1037,13 @@ int fcr_colreduce(const fcr_problem* problem, const void* q, const void* k, void
 
   cudaError_t e = cudaMemsetAsync(ws + pl.off_status, 0, kStatusWords * 4, stream);
   if (e != cudaSuccess) return cuda_fail(e, "cudaMemsetAsync");
+#ifdef FCR_PROFILE
+  {  // the two "earliest start" slots of the tuning counters start at the maximum
+    const unsigned long long big = ~0ULL;
+    cudaMemcpyAsync(ws + pl.off_status + 64 + 80 * 8, &big, 8, cudaMemcpyHostToDevice, stream);
+    cudaMemcpyAsync(ws + pl.off_status + 64 + 84 * 8, &big, 8, cudaMemcpyHostToDevice, stream);
+  }
+#endif
 
   // rows pass: Q stationary, K streamed
   trace_mark(0, stream);
