@@ -53,10 +53,11 @@ def flash_colreduce_host(
     if out.numel() == 0:
         return out
     if group_heads is None:
-        # groups of roughly 64 MiB of input: the first group's copy is the only one that is not
-        # hidden behind kernels, so it should be short; later groups are still large launches
+        # About eight groups per batch entry: the first group's copy is the only one that is not
+        # hidden behind kernels, so it should be a small share, yet every launch should still
+        # carry many heads.  Groups are capped at 512 MiB of input.
         per_head = (m + n) * d * query.element_size()
-        group_heads = max(1, min(h, (64 << 20) // max(per_head, 1)))
+        group_heads = max(1, min(-(-h // 8), (512 << 20) // max(per_head, 1)))
     groups = [(bi, h0, min(h0 + group_heads, h)) for bi in range(b) for h0 in range(0, h, group_heads)]
     with torch.cuda.device(device):
         compute = torch.cuda.current_stream(device)

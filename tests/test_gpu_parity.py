@@ -284,3 +284,24 @@ def test_capturable_in_a_cuda_graph():
     want = flash_colreduce(q, k, "mean", is_causal=True)
     assert torch.equal(captured, want)
     assert not torch.equal(captured, eager)
+
+
+def test_host_resident_inputs():
+    """flash_colreduce_host streams head groups through the GPU; result equals the device API's."""
+    from flash_colreduce_b200 import flash_colreduce, flash_colreduce_host
+
+    dev = _dev()
+    q, k = _rand((2, 6, 400, 64), 50), _rand((2, 6, 900, 64), 51)
+    want = oracle_colreduce(q, k, "mean", True)
+    for pinned in (False, True):
+        qh = q.pin_memory() if pinned else q
+        kh = k.pin_memory() if pinned else k
+        for group in (None, 1, 4, 6):
+            got = flash_colreduce_host(qh, kh, "mean", is_causal=True, device=dev, group_heads=group)
+            assert not got.is_cuda and got.shape == (2, 6, 900) and got.dtype == torch.float16
+            assert_parity(got, want, "mean", extra_rtol=2.0 ** -11)
+            assert torch.equal(got, flash_colreduce(q.to(dev), k.to(dev), "mean", is_causal=True).cpu())
+    with pytest.raises(ValueError, match="host tensors"):
+        flash_colreduce_host(q.to(dev), k.to(dev), "sum")
+    with pytest.raises(ValueError, match="Invalid reduction"):
+        flash_colreduce_host(q, k, "prod")
