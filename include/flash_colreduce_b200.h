@@ -80,13 +80,13 @@ typedef struct fcr_plan {
   int32_t d_pad;            /* head dimension the kernels run at: 64 or 128 (zero-filled by TMA) */
   int32_t rows_per_block;   /* stationary rows a CTA owns: 256 */
   int32_t m_pad, n_pad;     /* M and N rounded up to 128 */
-  int32_t row_blocks;       /* phase 1: blocks of query rows per head */
-  int32_t col_blocks;       /* phase 2: blocks of key columns per head */
-  int32_t row_splits;       /* phase 1: splits of the key range per row block */
-  int32_t col_splits;       /* phase 2: splits of the query range per column block */
-  int32_t row_items, col_items; /* work items per phase = B*H*blocks*splits */
-  int32_t row_ctas, col_ctas;   /* persistent CTAs launched per phase */
-  int32_t head_group;       /* heads whose work items are interleaved so that they share the L2 cache */
+  int32_t row_blocks;       /* rows pass: blocks of 256 query rows per head */
+  int32_t col_blocks;       /* columns pass: blocks of 256 key columns per head */
+  int32_t row_splits;       /* rows pass: splits of the key range per row block */
+  int32_t col_splits;       /* columns pass: splits of the query range per column block */
+  int32_t row_items, col_items; /* work items per pass = B*H*blocks*splits */
+  int32_t row_ctas, col_ctas;   /* persistent CTAs launched per pass */
+  int32_t head_group;       /* heads whose work items are interleaved (causal: evens out the tail of the grid) */
   int32_t short_items;      /* bit 0 / 1: the rows / columns pass uses the buffering for items of few tiles */
   int64_t causal_offset;    /* resolved offset */
   int64_t valid_scores;     /* B*H*sum_i valid(i): the unit the throughput metric counts */
