@@ -318,6 +318,10 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
   __syncthreads();
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  // Set-up is done: let the next kernel of the stream begin its own set-up as SMs free up,
+  // and wait here for the previous kernel's results (the rows pass's lse, the work counters).
+  if (threadIdx.x == 0) ptx::grid_launch_dependents();
+  ptx::grid_dependency_wait();
 
   if (warp == kProducerWarp) {
     // ------------------------------------------------------------ TMA warp
@@ -724,6 +728,8 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
 __global__ void combine_lse_kernel(const float* __restrict__ part_m,
                                    const float* __restrict__ part_l, float* __restrict__ neg_lse,
                                    int n_split, size_t per_split, int m_pad, int M) {
+  ptx::grid_launch_dependents();
+  ptx::grid_dependency_wait();
   const size_t total = per_split;
   for (size_t idx = blockIdx.x * (size_t)blockDim.x + threadIdx.x; idx < total;
        idx += (size_t)gridDim.x * blockDim.x) {
@@ -743,6 +749,7 @@ __global__ void combine_lse_kernel(const float* __restrict__ part_m,
 // Combines the per-split column partials in split order, applies the mean
 // divisor and casts (flash_colreduce/flash.py:308, :377-385).
 __global__ void final_reduce_kernel(const float* __restrict__ part, PassParams p, int is_max) {
+  ptx::grid_dependency_wait();
   const size_t per_split = (size_t)p.BH * p.n_pad;
   for (size_t idx = blockIdx.x * (size_t)blockDim.x + threadIdx.x; idx < per_split;
        idx += (size_t)gridDim.x * blockDim.x) {
@@ -895,6 +902,24 @@ static uint32_t instr_desc(int dtype, bool negate_a) {
          ((uint32_t)(kTile >> 3) << 17) | ((uint32_t)(kTile >> 4) << 24);
 }
 
+// Launches `kern`; with `dependent` it may begin while the previous kernel of the stream is
+// still running (the kernels call grid_dependency_wait() before reading its results).
+template <typename... KArgs, typename... Args>
+static cudaError_t launch_kernel(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                 cudaStream_t stream, bool dependent, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = dependent ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
 template <int PHASE, int DPAD, int RED, bool SHORT>
 static int launch_pass(const CUtensorMap& stat, const CUtensorMap& strm, const PassParams& pp,
                        int ctas, cudaStream_t stream) {
@@ -911,8 +936,9 @@ static int launch_pass(const CUtensorMap& stat, const CUtensorMap& strm, const P
     if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute");
     opted_in.fetch_or(bit, std::memory_order_release);
   }
-  kern<<<ctas, kThreads, smem, stream>>>(stat, strm, pp);
-  e = cudaGetLastError();
+  // the columns pass follows the rows pass (or its combine kernel) in the stream
+  e = launch_kernel(kern, dim3(ctas), dim3(kThreads), smem, stream, PHASE == PH_COLS, stat, strm, pp);
+  if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "pass kernel launch");
   return FCR_OK;
 }
@@ -1055,9 +1081,9 @@ int fcr_colreduce(const fcr_problem* problem, const void* q, const void* k, void
   if (pl.row_splits > 1) {
     const size_t per_split = (size_t)pp.BH * pl.m_pad;
     const int blocks = (int)std::min<size_t>((per_split + 255) / 256, 4096);
-    combine_lse_kernel<<<blocks, 256, 0, stream>>>(pp.part_m, pp.part_l, pp.neg_lse, pl.row_splits,
-                                                   per_split, pl.m_pad, pr.M);
-    e = cudaGetLastError();
+    e = launch_kernel(combine_lse_kernel, dim3(blocks), dim3(256), 0, stream, true, pp.part_m,
+                      pp.part_l, pp.neg_lse, pl.row_splits, per_split, pl.m_pad, pr.M);
+    if (e == cudaSuccess) e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "combine_lse launch");
   }
 
@@ -1078,8 +1104,9 @@ int fcr_colreduce(const fcr_problem* problem, const void* q, const void* k, void
   if (pl.col_splits > 1) {
     const size_t per_split = (size_t)pp.BH * pl.n_pad;
     const int blocks = (int)std::min<size_t>((per_split + 255) / 256, 4096);
-    final_reduce_kernel<<<blocks, 256, 0, stream>>>(pp.part_out, pp, pr.reduction == FCR_MAX);
-    e = cudaGetLastError();
+    e = launch_kernel(final_reduce_kernel, dim3(blocks), dim3(256), 0, stream, true, pp.part_out, pp,
+                      (int)(pr.reduction == FCR_MAX));
+    if (e == cudaSuccess) e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "final_reduce launch");
   }
   trace_mark(2, stream);
