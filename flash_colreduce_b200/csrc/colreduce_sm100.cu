@@ -54,7 +54,12 @@ constexpr int kColSplit = FCR_COLSPLIT;       // softmax warpgroups sharing one 
 constexpr int kSoftmaxWarps = 4 * kSubTiles * kColSplit;
 constexpr int kProducerWarp = kSoftmaxWarps;
 constexpr int kMmaWarp = kSoftmaxWarps + 1;   // issues the MMAs of sub-tile 0, owns the TMEM allocation
-constexpr int kMmaWarps = kSubTiles;          // one issuing warp per stationary sub-tile
+#ifndef FCR_MMA_PER_BUFFER
+#define FCR_MMA_PER_BUFFER 0
+#endif
+// MMA-issuing warps: one per stationary sub-tile, or one per accumulator buffer (two per sub-tile)
+constexpr bool kMmaPerBuffer = FCR_MMA_PER_BUFFER != 0;
+constexpr int kMmaWarps = kMmaPerBuffer ? 2 * kSubTiles : kSubTiles;
 constexpr int kThreads = (kSoftmaxWarps + 1 + kMmaWarps) * 32;
 constexpr int kTmemCols = 512;
 #ifndef FCR_TILE_OWNER
@@ -430,7 +435,8 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
     // drains during that warp's barrier handshakes; with two, one warp's
     // handshakes overlap the other's MMAs.
     PROF_DECL();
-    const int a = warp - kMmaWarp;
+    const int a = (warp - kMmaWarp) % kSubTiles;
+    const int my_buf = (warp - kMmaWarp) / kSubTiles;  // only with one issuer per accumulator buffer
     // Accumulator buffer of a tile = (its index within the work item + the item's parity) mod 2,
     // so that the warpgroup that folds it does not depend on which items this CTA happened to get;
     // tm_use[b] counts the uses of buffer b and gives its barrier phase.
@@ -454,8 +460,8 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
         const uint32_t s = ring_seq % KR, ph = (ring_seq / KR) & 1u;
         ok = WAIT(bar_ring_full(s), ph, ST_WAIT_RING_FULL);
         if (!ok) break;
-        if (t >= g.t_lo[a] && t < g.t_hi[a]) {
-          const uint32_t ts = (uint32_t)(t - g.t_lo[a] + g.par) & 1u;
+        const uint32_t ts = (uint32_t)(t - g.t_lo[a] + g.par) & 1u;
+        if (t >= g.t_lo[a] && t < g.t_hi[a] && (!kMmaPerBuffer || (int)ts == my_buf)) {
           const uint32_t tph = (ts ? tm_use[1] : tm_use[0]) & 1u;
           ok = WAIT(bar_tm_empty(a, ts), tph ^ 1u, ST_WAIT_TMEM_EMPTY);
           if (!ok) break;
