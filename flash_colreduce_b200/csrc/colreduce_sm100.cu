@@ -108,6 +108,8 @@ struct PassParams : PassGeom {
   int m_pad, n_pad;
   float scale2;    // |scale| * log2(e)
   uint32_t idesc;  // tcgen05 instruction descriptor
+  int tf32;        // fp32 operands multiplied as TF32 (else fp16 / bf16)
+  int slab_elems;  // elements per 128-byte operand slab: 64 (16-bit) or 32 (fp32)
   float* neg_lse;  // [BH][m_pad]
   float* part_m;   // [n_split][BH][m_pad]
   float* part_l;   // [n_split][BH][m_pad]
@@ -351,7 +353,7 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
 #pragma unroll
           for (int hf = 0; hf < L::kHalves; ++hf)
             ptx::tma_load_4d(s_stat + (ks * kSubTiles + a) * L::kTileBytes + hf * L::kHalfBytes,
-                             &tmap_stat, bar_stat_full(ks), hf * 64, g.r0[a], h, b);
+                             &tmap_stat, bar_stat_full(ks), hf * p.slab_elems, g.r0[a], h, b);
       }
       __syncwarp();
       return true;
@@ -414,7 +416,7 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
 #pragma unroll
           for (int hf = 0; hf < L::kHalves; ++hf)
             ptx::tma_load_4d(s_ring + s * L::kTileBytes + hf * L::kHalfBytes, &tmap_strm,
-                             bar_ring_full(s), hf * 64, t * kTile, h, b);
+                             bar_ring_full(s), hf * p.slab_elems, t * kTile, h, b);
           if (PHASE == PH_COLS)
             ptx::bulk_load(s_lse + s * L::kLseBytes,
                            p.neg_lse + (size_t)g.bh * p.m_pad + (size_t)t * kTile, L::kLseBytes,
@@ -473,8 +475,13 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
 #pragma unroll
             for (int kk = 0; kk < DPAD / 16; ++kk) {
               const uint32_t koff = (uint32_t)(kk >> 2) * L::kHalfBytes + (uint32_t)(kk & 3) * 32u;
-              ptx::umma_f16(d, ptx::smem_desc_sw128(a_addr + koff),
-                            ptx::smem_desc_sw128(b_addr + koff), p.idesc, kk > 0 ? 1u : 0u);
+              // every step consumes 32 bytes of each operand row: 16 halves or 8 TF32 values
+              if (p.tf32)
+                ptx::umma_tf32(d, ptx::smem_desc_sw128(a_addr + koff),
+                               ptx::smem_desc_sw128(b_addr + koff), p.idesc, kk > 0 ? 1u : 0u);
+              else
+                ptx::umma_f16(d, ptx::smem_desc_sw128(a_addr + koff),
+                              ptx::smem_desc_sw128(b_addr + koff), p.idesc, kk > 0 ? 1u : 0u);
             }
             ptx::umma_commit(bar_tm_full(a, ts));
             ptx::umma_commit(bar_ring_empty(s));
@@ -864,18 +871,21 @@ static int make_tensor_map(CUtensorMap* map, const void* ptr, int dtype, int D, 
   if (!enc) return fail(FCR_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
   if ((reinterpret_cast<uintptr_t>(ptr) & 15u) != 0)
     return fail(FCR_ERR_UNSUPPORTED, "q / k base address must be 16-byte aligned");
-  const int64_t fallback = align_up64((int64_t)D, 8);
+  const int elem_bytes = dtype == FCR_F32 ? 4 : 2;
+  const int align_elems = 16 / elem_bytes;
+  const int64_t fallback = align_up64((int64_t)D, align_elems);
   auto stride_bytes = [&](int dim, int64_t s) -> cuuint64_t {
-    if (dim <= 1 && (s <= 0 || s % 8 != 0)) s = fallback;  // never dereferenced
-    return (cuuint64_t)s * 2u;
+    if (dim <= 1 && (s <= 0 || s % align_elems != 0)) s = fallback;  // never dereferenced
+    return (cuuint64_t)s * (cuuint64_t)elem_bytes;
   };
   cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)rows, (cuuint64_t)H, (cuuint64_t)B};
   cuuint64_t gstr[3] = {stride_bytes(rows, strides[2]), stride_bytes(H, strides[1]),
                         stride_bytes(B, strides[0])};
-  cuuint32_t box[4] = {64u, (cuuint32_t)kTile, 1u, 1u};
+  cuuint32_t box[4] = {(cuuint32_t)(128 / elem_bytes), (cuuint32_t)kTile, 1u, 1u};  // 128-byte slab
   cuuint32_t estr[4] = {1u, 1u, 1u, 1u};
-  const CUtensorMapDataType dt =
-      dtype == FCR_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  const CUtensorMapDataType dt = dtype == FCR_F32    ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                 : dtype == FCR_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                     : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
   const CUresult r = enc(map, dt, 4, const_cast<void*>(ptr), dims, gstr, box, estr,
                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -902,8 +912,8 @@ static int device_sm_count(int* out) {
 }
 
 static uint32_t instr_desc(int dtype, bool negate_a) {
-  // kind::f16, fp32 accumulate, both operands K-major, M = 128, N = 128
-  const uint32_t fmt = dtype == FCR_BF16 ? 1u : 0u;
+  // kind::f16 / kind::tf32, fp32 accumulate, both operands K-major, M = 128, N = 128
+  const uint32_t fmt = dtype == FCR_F32 ? 2u : (dtype == FCR_BF16 ? 1u : 0u);
   return (1u << 4) | (fmt << 7) | (fmt << 10) | ((negate_a ? 1u : 0u) << 13) |
          ((uint32_t)(kTile >> 3) << 17) | ((uint32_t)(kTile >> 4) << 24);
 }
@@ -979,6 +989,8 @@ static void fill_common(PassParams& pp, const fcr_problem& pr, const fcr_plan& p
   if (!(s2 >= 1e-30f)) s2 = 1e-30f;  // scale 0: every score becomes (numerically) zero
   pp.scale2 = s2;
   pp.idesc = instr_desc(pr.in_dtype, pr.scale < 0.f);
+  pp.tf32 = pr.in_dtype == FCR_F32 ? 1 : 0;
+  pp.slab_elems = pr.in_dtype == FCR_F32 ? 32 : 64;
   pp.neg_lse = reinterpret_cast<float*>(ws + pl.off_neg_lse);
   pp.part_m = reinterpret_cast<float*>(ws + pl.off_part_m);
   pp.part_l = reinterpret_cast<float*>(ws + pl.off_part_l);

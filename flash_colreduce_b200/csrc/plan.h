@@ -162,12 +162,16 @@ inline int plan_problem(const fcr_problem& p, int num_sms, fcr_plan& pl, std::st
     err = "invalid reduction code " + std::to_string(p.reduction);
     return FCR_ERR_BAD_ARG;
   }
-  if (p.in_dtype != FCR_F16 && p.in_dtype != FCR_BF16) {
-    err = "q and k must be fp16 or bf16 (dtype code " + std::to_string(p.in_dtype) + ")";
+  if (p.in_dtype != FCR_F16 && p.in_dtype != FCR_BF16 && p.in_dtype != FCR_F32) {
+    err = "q and k must be fp16, bf16 or fp32 (dtype code " + std::to_string(p.in_dtype) + ")";
     return FCR_ERR_UNSUPPORTED;
   }
-  if (p.D > 128) {
-    err = "head dimension " + std::to_string(p.D) + " exceeds 128";
+  // An operand row may span at most 256 bytes (two 128-byte swizzled slabs).
+  const int elem_bytes = p.in_dtype == FCR_F32 ? 4 : 2;
+  const int align_elems = 16 / elem_bytes;  // strides must be multiples of 16 bytes
+  if (p.D * elem_bytes > 256) {
+    err = "head dimension " + std::to_string(p.D) + " exceeds " + std::to_string(256 / elem_bytes) +
+          (elem_bytes == 4 ? " (fp32 inputs run as TF32 with rows of at most 256 bytes)" : "");
     return FCR_ERR_UNSUPPORTED;
   }
   if (p.M > (1 << 30) || p.N > (1 << 30)) {
@@ -183,9 +187,9 @@ inline int plan_problem(const fcr_problem& p, int num_sms, fcr_plan& pl, std::st
     }
     const int32_t dims[3] = {p.B, p.H, t ? p.N : p.M};
     for (int a = 0; a < 3; ++a) {
-      if (dims[a] > 1 && (s[a] <= 0 || s[a] % 8 != 0)) {
+      if (dims[a] > 1 && (s[a] <= 0 || s[a] % align_elems != 0)) {
         err = std::string(name) + ": stride " + std::to_string(a) + " = " + std::to_string(s[a]) +
-              " is not a positive multiple of 8 elements (16 bytes)";
+              " is not a positive multiple of " + std::to_string(align_elems) + " elements (16 bytes)";
         return FCR_ERR_UNSUPPORTED;
       }
     }
@@ -204,7 +208,7 @@ inline int plan_problem(const fcr_problem& p, int num_sms, fcr_plan& pl, std::st
   }
   const int64_t BH = (int64_t)p.B * p.H;
 
-  pl.d_pad = p.D <= 64 ? 64 : 128;
+  pl.d_pad = p.D * elem_bytes <= 128 ? 64 : 128;  // row width in 2-byte units: 128 or 256 bytes
   pl.rows_per_block = kBlockRows;
   pl.m_pad = (int32_t)align_up64(p.M, kTile);
   pl.n_pad = (int32_t)align_up64(p.N, kTile);

@@ -29,17 +29,18 @@ def _tma_ready(x: torch.Tensor) -> torch.Tensor:
     """Returns ``x`` or a copy whose layout a TMA tensor map can describe.
 
     Needed: innermost stride 1, every other stride of a dimension longer than
-    one a positive multiple of 8 elements (16 bytes), 16-byte aligned base.
-    The head dimension is zero-padded to a multiple of 8 when it is not one,
+    one a positive multiple of 16 bytes, 16-byte aligned base.  The head
+    dimension is zero-padded to a multiple of 16 bytes when it is not one,
     which changes no dot product (the reference pads to a power of two for the
     same reason, flash_colreduce/flash.py:368-373).
     """
     d = x.shape[-1]
-    if d % 8 != 0:
-        x = torch.nn.functional.pad(x, (0, 8 - d % 8))
+    unit = 16 // x.element_size()  # elements per 16 bytes: 8 for fp16 / bf16, 4 for fp32
+    if d % unit != 0:
+        x = torch.nn.functional.pad(x, (0, unit - d % unit))
     ok = x.stride(3) == 1 and x.data_ptr() % 16 == 0
     for dim in range(3):
-        if x.shape[dim] > 1 and (x.stride(dim) <= 0 or x.stride(dim) % 8 != 0):
+        if x.shape[dim] > 1 and (x.stride(dim) <= 0 or x.stride(dim) % unit != 0):
             ok = False
     return x if ok else x.contiguous()
 
@@ -91,12 +92,15 @@ def _validate(query: torch.Tensor, key: torch.Tensor, reduction: str) -> None:
         )
     if reduction not in ["sum", "mean", "max"]:
         raise ValueError(f"Invalid reduction: {reduction}. Must be 'sum', 'mean', or 'max'.")
-    if query.dtype != key.dtype or query.dtype not in (torch.float16, torch.bfloat16):
+    if query.dtype != key.dtype or query.dtype not in _DTYPE_CODES:
         raise TypeError(
-            f"flash_colreduce runs fp16 or bf16 tensor-core kernels; got query {query.dtype}, key {key.dtype}."
+            f"flash_colreduce takes fp16, bf16 or fp32 (run as TF32) tensors of one dtype; "
+            f"got query {query.dtype}, key {key.dtype}."
         )
-    if query.shape[-1] > 128:
-        raise ValueError(f"Head dimension {query.shape[-1]} exceeds 128, the largest the sm_100a kernels take.")
+    d_max = 256 // query.element_size()
+    if query.shape[-1] > d_max:
+        raise ValueError(f"Head dimension {query.shape[-1]} exceeds {d_max}, the largest the sm_100a kernels take "
+                         f"for {query.dtype} (operand rows of at most 256 bytes).")
 
 
 def flash_colreduce(
@@ -117,7 +121,8 @@ def flash_colreduce(
     columns, then ``N - n``).
 
     Args:
-        query: (B, H, M, D) fp16 or bf16 CUDA tensor.
+        query: (B, H, M, D) CUDA tensor: fp16 or bf16 with D <= 128, or fp32 with D <= 64
+            (fp32 operands are multiplied as TF32, like the reference's tl.dot).
         key: (B, H, N, D), same dtype and device.
         reduction: "sum", "mean" or "max".
         is_causal: apply the right-aligned causal mask.

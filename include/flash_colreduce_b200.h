@@ -45,8 +45,8 @@ typedef enum fcr_reduction { FCR_SUM = 0, FCR_MEAN = 1, FCR_MAX = 2 } fcr_reduct
 /*
  * One column-reduction problem.  Strides are in ELEMENTS, in (B,H,rows,D)
  * order, exactly the four numbers `tensor.stride()` returns; the innermost
- * stride must be 1 and the other three must be multiples of 8 elements
- * (16 bytes) -- a TMA tensor-map requirement.
+ * stride must be 1 and the other three must be multiples of 16 bytes (8
+ * 16-bit or 4 fp32 elements) -- a TMA tensor-map requirement.
  *
  * Replaces the argument list of `_flash_colreduce_kernel`
  * (flash_colreduce/flash.py:145-167: pointers, scale, eight strides, H, M, N,
@@ -56,7 +56,7 @@ typedef struct fcr_problem {
   int32_t B, H, M, N, D;
   int64_t q_strides[4];
   int64_t k_strides[4];
-  int32_t in_dtype;      /* fcr_dtype of q and k: FCR_F16 or FCR_BF16 */
+  int32_t in_dtype;      /* fcr_dtype of q and k: FCR_F16, FCR_BF16 (D <= 128) or FCR_F32 (D <= 64, multiplied as TF32) */
   int32_t reduction;     /* fcr_reduction */
   int32_t is_causal;     /* 0 / 1 */
   float scale;           /* softmax scale applied to q.k (the reference's default is 1/sqrt(D)) */

@@ -77,7 +77,8 @@ def test_causal_offset_defaults_to_right_alignment():
     [
         (dict(m=0), nat.FCR_ERR_BAD_ARG, "positive"),
         (dict(d=129), nat.FCR_ERR_UNSUPPORTED, "exceeds 128"),
-        (dict(dtype=nat.FCR_F32), nat.FCR_ERR_UNSUPPORTED, "fp16 or bf16"),
+        (dict(dtype=nat.FCR_F32, d=72), nat.FCR_ERR_UNSUPPORTED, "exceeds 64"),
+        (dict(dtype=5), nat.FCR_ERR_UNSUPPORTED, "fp16, bf16 or fp32"),
         (dict(red=7), nat.FCR_ERR_BAD_ARG, "invalid reduction"),
         (dict(qs=(0, 0, 72, 2)), nat.FCR_ERR_UNSUPPORTED, "innermost stride"),
         (dict(qs=(0, 0, 20, 1)), nat.FCR_ERR_UNSUPPORTED, "multiple of 8"),

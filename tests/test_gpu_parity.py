@@ -243,7 +243,11 @@ def test_errors_match_the_reference_messages():
     with pytest.raises(ValueError, match="Invalid reduction: prod"):
         flash_colreduce(q, q, "prod")
     with pytest.raises(TypeError):
-        flash_colreduce(q.float(), q.float(), "sum")
+        flash_colreduce(q.double(), q.double(), "sum")
+    with pytest.raises(TypeError):
+        flash_colreduce(q, q.float(), "sum")
+    with pytest.raises(ValueError, match="exceeds 64"):
+        flash_colreduce(torch.zeros(1, 1, 8, 72, device=dev), torch.zeros(1, 1, 8, 72, device=dev), "sum")
     assert flash_colreduce(q[:, :, :0], q, "sum").shape == (1, 2, 8)
     assert flash_colreduce(q, q[:, :, :0], "sum").shape == (1, 2, 0)
 
@@ -305,3 +309,24 @@ def test_host_resident_inputs():
         flash_colreduce_host(q.to(dev), k.to(dev), "sum")
     with pytest.raises(ValueError, match="Invalid reduction"):
         flash_colreduce_host(q, k, "prod")
+
+
+def _tf32(x: torch.Tensor) -> torch.Tensor:
+    """fp32 values with the 13 low mantissa bits cleared: exactly representable as TF32."""
+    return (x.contiguous().view(torch.int32) & ~0x1FFF).view(torch.float32)
+
+
+@pytest.mark.parametrize("d", [16, 32, 40, 64])
+def test_float32_inputs_run_as_tf32(d):
+    """fp32 tensors (the reference multiplies them as TF32 in tl.dot, flash.py:59) against the oracle
+    on the same TF32-representable values; the result dtype is fp32."""
+    from flash_colreduce_b200 import flash_colreduce
+
+    dev = _dev()
+    q = _tf32(_rand((2, 3, 300, d), 60, torch.float32))
+    k = _tf32(_rand((2, 3, 500, d), 61, torch.float32))
+    for red in ("sum", "mean", "max"):
+        for causal in (False, True):
+            got = flash_colreduce(q.to(dev), k.to(dev), red, is_causal=causal)
+            assert got.dtype == torch.float32
+            assert_parity(got, oracle_colreduce(q, k, red, causal), red)
