@@ -37,6 +37,7 @@
 #include <atomic>
 #include <mutex>
 #include <string>
+#include <type_traits>
 #include <vector>
 
 #include "plan.h"
@@ -132,8 +133,9 @@ struct SmemLayout {
   static constexpr int kTileBytes = kTile * DPAD * 2;
   static constexpr int kHalves = DPAD / 64;     // 64-element (128-byte) column slabs per tile
   static constexpr int kHalfBytes = kTile * 128;
-  static constexpr int KS = (DPAD == 64 || SHORT) ? 2 : 1;  // stationary stages (items in flight)
-  static constexpr int KR = (DPAD == 64) ? 6 : (SHORT ? 2 : 4);  // streamed ring stages
+  // 512-byte rows (DPAD 256) leave room for one stage of each only: correct, not fast.
+  static constexpr int KS = DPAD == 256 ? 1 : ((DPAD == 64 || SHORT) ? 2 : 1);  // stationary stages
+  static constexpr int KR = DPAD == 256 ? 1 : (DPAD == 64 ? 6 : (SHORT ? 2 : 4));  // streamed ring stages
   static constexpr int kLseBytes = kTile * 4;
   static constexpr int off_stat = 0;
   static constexpr int off_ring = off_stat + KS * kSubTiles * kTileBytes;
@@ -295,9 +297,7 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
     }
     for (int i = 0; i < KR; ++i) {
       ptx::mbar_init(bar_ring_full(i), 1);
-      ptx::mbar_init(bar_ring_empty(i),
-                     PHASE != PH_COLS ? kMmaWarps
-                                      : kMmaWarps + (kTileOwner ? 4 * kSubTiles : kSoftmaxWarps));
+      ptx::mbar_init(bar_ring_empty(i), PHASE != PH_COLS ? kMmaWarps : kMmaWarps + kSoftmaxWarps);
     }
     for (int a = 0; a < 2; ++a)
       for (int ts = 0; ts < 2; ++ts) {
@@ -472,17 +472,24 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
           if (lane == 0) {
             const uint32_t d = tmem_base + (uint32_t)(a * 2 + ts) * kTile;
             const uint32_t b_addr = s_ring + s * L::kTileBytes;
+            // One instruction per 32 bytes of each operand row: 16 halves or 8 TF32 values.
+            // The operand kind is chosen once, outside the unrolled sequence.
+            auto issue_steps = [&](auto as_tf32) {
 #pragma unroll
-            for (int kk = 0; kk < DPAD / 16; ++kk) {
-              const uint32_t koff = (uint32_t)(kk >> 2) * L::kHalfBytes + (uint32_t)(kk & 3) * 32u;
-              // every step consumes 32 bytes of each operand row: 16 halves or 8 TF32 values
-              if (p.tf32)
-                ptx::umma_tf32(d, ptx::smem_desc_sw128(a_addr + koff),
-                               ptx::smem_desc_sw128(b_addr + koff), p.idesc, kk > 0 ? 1u : 0u);
-              else
-                ptx::umma_f16(d, ptx::smem_desc_sw128(a_addr + koff),
-                              ptx::smem_desc_sw128(b_addr + koff), p.idesc, kk > 0 ? 1u : 0u);
-            }
+              for (int kk = 0; kk < DPAD / 16; ++kk) {
+                const uint32_t koff = (uint32_t)(kk >> 2) * L::kHalfBytes + (uint32_t)(kk & 3) * 32u;
+                if constexpr (decltype(as_tf32)::value)
+                  ptx::umma_tf32(d, ptx::smem_desc_sw128(a_addr + koff),
+                                 ptx::smem_desc_sw128(b_addr + koff), p.idesc, kk > 0 ? 1u : 0u);
+                else
+                  ptx::umma_f16(d, ptx::smem_desc_sw128(a_addr + koff),
+                                ptx::smem_desc_sw128(b_addr + koff), p.idesc, kk > 0 ? 1u : 0u);
+              }
+            };
+            if (p.tf32)
+              issue_steps(std::true_type{});
+            else
+              issue_steps(std::false_type{});
             ptx::umma_commit(bar_tm_full(a, ts));
             ptx::umma_commit(bar_ring_empty(s));
           }
@@ -563,10 +570,11 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
         // with tile ownership a warpgroup folds every other tile of its sub-tile
         const bool active = in_range && (!kTileOwner || (int)ts == part);
         const uint32_t s = rs % KR, rph = (rs / KR) & 1u;
-        // columns pass: the ring slot also carries the tile's lse values; it is released by the
-        // warps that read them (or, for a tile the sub-tile skips, by the warpgroup of its parity)
-        const bool holds_slot =
-            PHASE == PH_COLS && (!kTileOwner || active || (!in_range && (t & 1) == part));
+        // columns pass: the ring slot also carries the tile's lse values, which the folding
+        // warps read.  Every softmax warp waits for every slot and releases it, whether or not
+        // it folds the tile: a warp that skipped phases of a barrier could pass a later
+        // parity wait on a stale phase and release the slot before it had been filled.
+        constexpr bool holds_slot = PHASE == PH_COLS;
         if (holds_slot) {
           ok = WAIT(bar_ring_full(s), rph, ST_WAIT_RING_FULL_SM);
           if (!ok) break;
@@ -964,6 +972,7 @@ static int launch_pass_d(int d_pad, bool short_items, const CUtensorMap& stat,
                          const CUtensorMap& strm, const PassParams& pp, int ctas,
                          cudaStream_t stream) {
   if (d_pad == 64) return launch_pass<PHASE, 64, RED, false>(stat, strm, pp, ctas, stream);
+  if (d_pad == 256) return launch_pass<PHASE, 256, RED, false>(stat, strm, pp, ctas, stream);
   if (short_items) return launch_pass<PHASE, 128, RED, true>(stat, strm, pp, ctas, stream);
   return launch_pass<PHASE, 128, RED, false>(stat, strm, pp, ctas, stream);
 }

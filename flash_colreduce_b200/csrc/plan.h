@@ -166,12 +166,12 @@ inline int plan_problem(const fcr_problem& p, int num_sms, fcr_plan& pl, std::st
     err = "q and k must be fp16, bf16 or fp32 (dtype code " + std::to_string(p.in_dtype) + ")";
     return FCR_ERR_UNSUPPORTED;
   }
-  // An operand row may span at most 256 bytes (two 128-byte swizzled slabs).
+  // An operand row may span at most 512 bytes (four 128-byte swizzled slabs).
   const int elem_bytes = p.in_dtype == FCR_F32 ? 4 : 2;
   const int align_elems = 16 / elem_bytes;  // strides must be multiples of 16 bytes
-  if (p.D * elem_bytes > 256) {
-    err = "head dimension " + std::to_string(p.D) + " exceeds " + std::to_string(256 / elem_bytes) +
-          (elem_bytes == 4 ? " (fp32 inputs run as TF32 with rows of at most 256 bytes)" : "");
+  if (p.D * elem_bytes > 512) {
+    err = "head dimension " + std::to_string(p.D) + " exceeds " + std::to_string(512 / elem_bytes) +
+          " (operand rows of at most 512 bytes)";
     return FCR_ERR_UNSUPPORTED;
   }
   if (p.M > (1 << 30) || p.N > (1 << 30)) {
@@ -208,7 +208,8 @@ inline int plan_problem(const fcr_problem& p, int num_sms, fcr_plan& pl, std::st
   }
   const int64_t BH = (int64_t)p.B * p.H;
 
-  pl.d_pad = p.D * elem_bytes <= 128 ? 64 : 128;  // row width in 2-byte units: 128 or 256 bytes
+  // row width the kernels run at, in 2-byte units: 128, 256 or 512 bytes
+  pl.d_pad = p.D * elem_bytes <= 128 ? 64 : (p.D * elem_bytes <= 256 ? 128 : 256);
   pl.rows_per_block = kBlockRows;
   pl.m_pad = (int32_t)align_up64(p.M, kTile);
   pl.n_pad = (int32_t)align_up64(p.N, kTile);

@@ -97,10 +97,10 @@ def _validate(query: torch.Tensor, key: torch.Tensor, reduction: str) -> None:
             f"flash_colreduce takes fp16, bf16 or fp32 (run as TF32) tensors of one dtype; "
             f"got query {query.dtype}, key {key.dtype}."
         )
-    d_max = 256 // query.element_size()
+    d_max = 512 // query.element_size()
     if query.shape[-1] > d_max:
         raise ValueError(f"Head dimension {query.shape[-1]} exceeds {d_max}, the largest the sm_100a kernels take "
-                         f"for {query.dtype} (operand rows of at most 256 bytes).")
+                         f"for {query.dtype} (operand rows of at most 512 bytes).")
 
 
 def flash_colreduce(
@@ -121,8 +121,9 @@ def flash_colreduce(
     columns, then ``N - n``).
 
     Args:
-        query: (B, H, M, D) CUDA tensor: fp16 or bf16 with D <= 128, or fp32 with D <= 64
-            (fp32 operands are multiplied as TF32, like the reference's tl.dot).
+        query: (B, H, M, D) CUDA tensor: fp16 or bf16 with D <= 256, or fp32 with D <= 128
+            (fp32 operands are multiplied as TF32, like the reference's tl.dot).  Rows of up to
+            256 bytes (D <= 128 in 16 bits) run the fast path.
         key: (B, H, N, D), same dtype and device.
         reduction: "sum", "mean" or "max".
         is_causal: apply the right-aligned causal mask.

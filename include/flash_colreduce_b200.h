@@ -56,7 +56,7 @@ typedef struct fcr_problem {
   int32_t B, H, M, N, D;
   int64_t q_strides[4];
   int64_t k_strides[4];
-  int32_t in_dtype;      /* fcr_dtype of q and k: FCR_F16, FCR_BF16 (D <= 128) or FCR_F32 (D <= 64, multiplied as TF32) */
+  int32_t in_dtype;      /* fcr_dtype of q and k: FCR_F16, FCR_BF16 (D <= 256) or FCR_F32 (D <= 128, multiplied as TF32) */
   int32_t reduction;     /* fcr_reduction */
   int32_t is_causal;     /* 0 / 1 */
   float scale;           /* softmax scale applied to q.k (the reference's default is 1/sqrt(D)) */
@@ -77,7 +77,7 @@ typedef struct fcr_problem {
 
 /* Launch plan derived on the host from a problem and an SM count. */
 typedef struct fcr_plan {
-  int32_t d_pad;            /* head dimension the kernels run at: 64 or 128 (zero-filled by TMA) */
+  int32_t d_pad;            /* row width the kernels run at, in 2-byte units: 64, 128 or 256 (zero-filled by TMA) */
   int32_t rows_per_block;   /* stationary rows a CTA owns: 256 */
   int32_t m_pad, n_pad;     /* M and N rounded up to 128 */
   int32_t row_blocks;       /* rows pass: blocks of 256 query rows per head */

@@ -46,7 +46,7 @@ def test_plan_counts_valid_scores(cfg, scores):
     b, h, m, n, d, causal = cfg
     pl = nat.plan(_problem(b, h, m, n, d, causal=causal), 148)
     assert pl.valid_scores == scores
-    assert pl.d_pad == (64 if d <= 64 else 128)
+    assert pl.d_pad == (64 if d <= 64 else 128 if d <= 128 else 256)
     assert pl.m_pad % 128 == 0 and pl.m_pad >= m and pl.n_pad % 128 == 0 and pl.n_pad >= n
     assert pl.row_items == b * h * pl.row_blocks * pl.row_splits
     assert pl.col_items == b * h * pl.col_blocks * pl.col_splits
@@ -76,8 +76,8 @@ def test_causal_offset_defaults_to_right_alignment():
     "kwargs,status,text",
     [
         (dict(m=0), nat.FCR_ERR_BAD_ARG, "positive"),
-        (dict(d=129), nat.FCR_ERR_UNSUPPORTED, "exceeds 128"),
-        (dict(dtype=nat.FCR_F32, d=72), nat.FCR_ERR_UNSUPPORTED, "exceeds 64"),
+        (dict(d=264), nat.FCR_ERR_UNSUPPORTED, "exceeds 256"),
+        (dict(dtype=nat.FCR_F32, d=132), nat.FCR_ERR_UNSUPPORTED, "exceeds 128"),
         (dict(dtype=5), nat.FCR_ERR_UNSUPPORTED, "fp16, bf16 or fp32"),
         (dict(red=7), nat.FCR_ERR_BAD_ARG, "invalid reduction"),
         (dict(qs=(0, 0, 72, 2)), nat.FCR_ERR_UNSUPPORTED, "innermost stride"),

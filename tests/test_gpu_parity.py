@@ -169,11 +169,23 @@ def test_more_queries_than_keys_and_edge_shapes(m, n):
 
 
 @pytest.mark.parametrize("b,h,m,n,d", [(1, 1, 1, 1, 8), (3, 5, 1, 7, 8), (2, 2, 7, 1, 24), (16, 64, 2, 3, 16),
-                                       (1, 2, 129, 255, 120), (1, 1, 257, 129, 104), (1, 3, 640, 384, 128)])
+                                       (1, 2, 129, 255, 120), (1, 1, 257, 129, 104), (1, 3, 640, 384, 128),
+                                       (1, 2, 300, 700, 256), (2, 1, 1100, 513, 192), (1, 3, 257, 2049, 136)])
 def test_degenerate_and_odd_head_dims(b, h, m, n, d):
     dev = _dev()
     q, k = _rand((b, h, m, d), 30), _rand((b, h, n, d), 31)
     for red in ("sum", "mean", "max"):
+        for causal in (False, True):
+            assert_parity(_f32(q.to(dev), k.to(dev), red, causal), oracle_colreduce(q, k, red, causal), red)
+
+
+@pytest.mark.parametrize("d", [64, 128, 192])
+def test_many_items_per_cta_with_a_skipped_half_block(d):
+    """More work items than CTAs, several streamed tiles per item, and a last key block whose
+    second half lies beyond N: every CTA runs items of both kinds back to back."""
+    dev = _dev()
+    q, k = _rand((4, 64, 300, d), 40), _rand((4, 64, 300, d), 41)
+    for red in ("sum", "max"):
         for causal in (False, True):
             assert_parity(_f32(q.to(dev), k.to(dev), red, causal), oracle_colreduce(q, k, red, causal), red)
 
@@ -246,8 +258,8 @@ def test_errors_match_the_reference_messages():
         flash_colreduce(q.double(), q.double(), "sum")
     with pytest.raises(TypeError):
         flash_colreduce(q, q.float(), "sum")
-    with pytest.raises(ValueError, match="exceeds 64"):
-        flash_colreduce(torch.zeros(1, 1, 8, 72, device=dev), torch.zeros(1, 1, 8, 72, device=dev), "sum")
+    with pytest.raises(ValueError, match="exceeds 128"):
+        flash_colreduce(torch.zeros(1, 1, 8, 136, device=dev), torch.zeros(1, 1, 8, 136, device=dev), "sum")
     assert flash_colreduce(q[:, :, :0], q, "sum").shape == (1, 2, 8)
     assert flash_colreduce(q, q[:, :, :0], "sum").shape == (1, 2, 0)
 
@@ -316,7 +328,7 @@ def _tf32(x: torch.Tensor) -> torch.Tensor:
     return (x.contiguous().view(torch.int32) & ~0x1FFF).view(torch.float32)
 
 
-@pytest.mark.parametrize("d", [16, 32, 40, 64])
+@pytest.mark.parametrize("d", [16, 32, 40, 64, 96, 128])
 def test_float32_inputs_run_as_tf32(d):
     """fp32 tensors (the reference multiplies them as TF32 in tl.dot, flash.py:59) against the oracle
     on the same TF32-representable values; the result dtype is fp32."""
