@@ -122,6 +122,8 @@ struct PassParams : PassGeom {
   int div_M, div_N, div_c;
   int* status;
   int* sched_counter;  // zero at launch; hands out work items beyond the first gridDim.x
+  int key_tiles;       // key-streaming kernels: 128-key tiles per head
+  int fold_cols;       // key-streaming columns pass: M rounded up to a 32-query chunk
 };
 
 // SHORT selects the buffering for work items that stream only a few tiles: two stationary
@@ -745,6 +747,10 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
 #endif
 }
 
+}  // namespace fcr
+#include "keystream_sm100.cuh"
+namespace fcr {
+
 // Combines the per-split running (max, sum) of the rows pass into -lse.
 __global__ void combine_lse_kernel(const float* __restrict__ part_m,
                                    const float* __restrict__ part_l, float* __restrict__ neg_lse,
@@ -977,6 +983,34 @@ static int launch_pass_d(int d_pad, bool short_items, const CUtensorMap& stat,
   return launch_pass<PHASE, 128, RED, false>(stat, strm, pp, ctas, stream);
 }
 
+template <int PHASE, int DPAD, int RED>
+static int launch_keystream(const CUtensorMap& map_q, const CUtensorMap& map_k, const PassParams& pp,
+                            int ctas, cudaStream_t stream) {
+  auto kern = keystream_kernel<PHASE, DPAD, RED>;
+  constexpr int smem = KeyStreamSmem<DPAD>::kDynamicBytes;
+  static std::atomic<unsigned long long> opted_in{0};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+  const unsigned long long bit = 1ULL << (dev & 63);
+  if (!(opted_in.load(std::memory_order_acquire) & bit)) {
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute");
+    opted_in.fetch_or(bit, std::memory_order_release);
+  }
+  e = launch_kernel(kern, dim3(ctas), dim3(kKsThreads), smem, stream, PHASE == PH_COLS, map_q, map_k, pp);
+  if (e == cudaSuccess) e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "key-streaming kernel launch");
+  return FCR_OK;
+}
+
+template <int PHASE, int RED>
+static int launch_keystream_d(int d_pad, const CUtensorMap& map_q, const CUtensorMap& map_k,
+                              const PassParams& pp, int ctas, cudaStream_t stream) {
+  if (d_pad == 64) return launch_keystream<PHASE, 64, RED>(map_q, map_k, pp, ctas, stream);
+  return launch_keystream<PHASE, 128, RED>(map_q, map_k, pp, ctas, stream);
+}
+
 static int check_workspace(const fcr_plan& pl, const void* ws, size_t ws_bytes) {
   if (!ws) return fail(FCR_ERR_WORKSPACE, "workspace is null");
   if ((reinterpret_cast<uintptr_t>(ws) & 255u) != 0)
@@ -1049,6 +1083,13 @@ int fcr_plan_item(const fcr_problem* problem, const fcr_plan* plan, int32_t pass
   if (pass != 1 && pass != 2) return fail(FCR_ERR_BAD_ARG, "pass must be 1 (rows) or 2 (columns)");
   const PassGeom g = pass_geometry(*problem, *plan, pass == 2);
   if (item < 0 || item >= g.n_items) return fail(FCR_ERR_BAD_ARG, "item out of range");
+  if (plan->key_stream) {
+    int bh, sp, t_lo, t_hi;
+    keystream_item(plan->key_chunks, plan->n_pad / kTile, item, bh, sp, t_lo, t_hi);
+    const int32_t v[10] = {bh, sp, t_lo, t_hi, 0, t_lo, t_hi, plan->m_pad, t_lo, t_lo};
+    memcpy(out, v, sizeof(v));
+    return FCR_OK;
+  }
   const Item it = pass == 2 ? decode_item<true>(g, item) : decode_item<false>(g, item);
   out[0] = it.bh;
   out[1] = it.sp;
@@ -1097,6 +1138,43 @@ int fcr_colreduce(const fcr_problem* problem, const void* q, const void* k, void
     cudaMemcpyAsync(ws + pl.off_status + 64 + 84 * 8, &big, 8, cudaMemcpyHostToDevice, stream);
   }
 #endif
+
+  if (pl.key_stream) {
+    // Decode shapes: both passes stream the key tiles past the head's one query tile.
+    trace_mark(0, stream);
+    PassParams pp;
+    auto fill = [&](bool cols) {
+      fill_common(pp, pr, pl, ws, cols);
+      pp.n_split = pl.key_chunks;
+      pp.n_items = pl.row_items;
+      pp.key_tiles = pl.n_pad / kTile;
+      pp.fold_cols = (int)align_up64(pr.M, kChunkCols);
+    };
+    fill(false);
+    rc = launch_keystream_d<PH_ROWS, RED_SUM>(pl.d_pad, map_q, map_k, pp, pl.row_ctas, stream);
+    if (rc != FCR_OK) return rc;
+    {
+      const size_t per_split = (size_t)pp.BH * pl.m_pad;
+      const int blocks = (int)std::min<size_t>((per_split + 255) / 256, 4096);
+      e = launch_kernel(combine_lse_kernel, dim3(blocks), dim3(256), 0, stream, true, pp.part_m,
+                        pp.part_l, pp.neg_lse, pl.row_splits, per_split, pl.m_pad, pr.M);
+      if (e == cudaSuccess) e = cudaGetLastError();
+      if (e != cudaSuccess) return cuda_fail(e, "combine_lse launch");
+    }
+    trace_mark(1, stream);
+    fill(true);
+    pp.out = out;
+    pp.out_dtype = out_dtype;
+    fill_mean(pp, pr.reduction, pr.is_causal, pr.mean_M > 0 ? pr.mean_M : pr.M,
+              pr.mean_N > 0 ? pr.mean_N : pr.N);
+    if (pr.reduction == FCR_MAX)
+      rc = launch_keystream_d<PH_COLS, RED_MAX>(pl.d_pad, map_q, map_k, pp, pl.col_ctas, stream);
+    else
+      rc = launch_keystream_d<PH_COLS, RED_SUM>(pl.d_pad, map_q, map_k, pp, pl.col_ctas, stream);
+    if (rc != FCR_OK) return rc;
+    trace_mark(2, stream);
+    return FCR_OK;
+  }
 
   // rows pass: Q stationary, K streamed
   trace_mark(0, stream);

@@ -47,6 +47,15 @@ struct Item {
   int c_lo, c_hi;
 };
 
+// Key streaming: work item `item` of either pass is chunk item % S of head item / S and covers
+// key tiles [key_tiles * sp / S, key_tiles * (sp + 1) / S) of that head.
+FCR_HD void keystream_item(int S, int key_tiles, int item, int& bh, int& sp, int& t_lo, int& t_hi) {
+  bh = item / S;
+  sp = item - bh * S;
+  t_lo = (int)(((long long)key_tiles * sp) / S);
+  t_hi = (int)(((long long)key_tiles * (sp + 1)) / S);
+}
+
 template <typename T>
 FCR_HD T hd_min(T a, T b) { return a < b ? a : b; }
 template <typename T>
@@ -244,6 +253,38 @@ inline int plan_problem(const fcr_problem& p, int num_sms, fcr_plan& pl, std::st
                    (ceil_div64(col_len, pl.col_splits) <= 8 ? 2 : 0);
   pl.row_ctas = (int32_t)std::min<int64_t>(row_items, num_sms);
   pl.col_ctas = (int32_t)std::min<int64_t>(col_items, num_sms);
+
+  // Decode shapes: every query of a head fits one tile and the keys are long.  Both passes then
+  // stream the key tiles (see keystream_item); CTA c runs items [c*I/G, (c+1)*I/G), so S is
+  // chosen to minimise the longest CTA: items per CTA times (tiles per item + one tile of
+  // per-item overhead).
+  pl.key_stream = 0;
+  pl.key_chunks = 0;
+  const int64_t key_tiles = pl.n_pad / kTile;
+  if (pl.m_pad == kTile && key_tiles >= 8 && pl.d_pad <= 128) {
+    int best_s = 1;
+    int64_t best_cost = -1;
+    for (int64_t s = 1; s <= std::min<int64_t>(key_tiles, 256); ++s) {
+      const int64_t per_cta = ceil_div64(BH * s, num_sms);
+      const int64_t cost = per_cta * (ceil_div64(key_tiles, s) + 1);
+      if (best_cost < 0 || cost < best_cost) {
+        best_cost = cost;
+        best_s = (int)s;
+      }
+    }
+    if (BH * best_s > (1LL << 30)) {
+      err = "problem has too many work items";
+      return FCR_ERR_UNSUPPORTED;
+    }
+    pl.key_stream = 1;
+    pl.key_chunks = best_s;
+    pl.row_splits = 4 * best_s;  // one partial state per chunk and softmax warpgroup
+    pl.col_splits = 1;
+    pl.row_items = pl.col_items = (int32_t)(BH * best_s);
+    pl.row_ctas = pl.col_ctas = (int32_t)std::min<int64_t>(pl.row_items, num_sms);
+    pl.head_group = 1;
+    pl.short_items = 0;
+  }
 
   int64_t scores = 0;
   if (!causal) {

@@ -97,6 +97,12 @@ typedef struct fcr_plan {
   int64_t off_part_l;       /* float[row_splits][B*H][m_pad] running sums   (row_splits > 1) */
   int64_t off_part_out;     /* float[col_splits][B*H][n_pad] column partials (col_splits > 1) */
   int64_t workspace_bytes;
+  /* Key streaming (M <= 128 and at least 8 key tiles, the decode shapes): both passes keep the one
+   * query tile of a head in shared memory and stream its key tiles through a deep ring.  The key
+   * tiles of a head are cut into key_chunks equal chunks, one work item each; the rows pass leaves
+   * row_splits = 4 * key_chunks partial (max, sum) states per row, the columns pass none. */
+  int32_t key_stream;       /* 1 when the key-streaming kernels run this problem */
+  int32_t key_chunks;       /* work items per head and pass */
 } fcr_plan;
 
 /* Library version string, e.g. "0.1.0". */
@@ -120,6 +126,11 @@ int fcr_plan_problem(const fcr_problem* problem, int32_t num_sms, fcr_plan* plan
  * tile_lo_b, tile_hi_b}: 128-row streamed tiles [tile_lo, tile_hi) are
  * multiplied against the stationary tile starting at row0.  This is the
  * counterpart of the per-program loop bounds of flash_colreduce/flash.py:201-207.
+ * For a key-streaming plan both passes report {head, chunk, key_tile_lo,
+ * key_tile_hi, 0, key_tile_lo, key_tile_hi, m_pad, key_tile_lo, key_tile_lo}:
+ * key tiles [lo, hi) of the head against its single query tile; tile t of the
+ * item is folded by warpgroup (t - key_tile_lo) mod 4, and the rows pass
+ * stores that warpgroup's state in partial slot 4 * chunk + warpgroup.
  */
 int fcr_plan_item(const fcr_problem* problem, const fcr_plan* plan, int32_t pass, int32_t item,
                   int32_t* out);

@@ -42,15 +42,23 @@ def emulate(q: torch.Tensor, k: torch.Tensor, reduction: str, is_causal: bool, s
     part_l = torch.zeros((pl.row_splits, B * H, pl.m_pad))
     for item in range(pl.row_items):
         it = nat.plan_item(prob, pl, 1, item)
-        bh, sp = it["head"], it["split"]
-        for (r0, t_lo, t_hi) in it["sub"]:
+        bh = it["head"]
+        if pl.key_stream:
+            # key streaming: warpgroup w folds tiles t_lo + w, t_lo + w + 4, ... into partial slot 4 * chunk + w
+            lo, hi = it["chunk"]
+            assert it["sub"][0] == (0, lo, hi) and it["sub"][1][1] == it["sub"][1][2]
+            walks = [(4 * it["split"] + w, 0, list(range(lo + w, hi, 4))) for w in range(4)]
+        else:
+            walks = [(it["split"], r0, list(range(t_lo, t_hi))) for (r0, t_lo, t_hi) in it["sub"]]
+            for (r0, t_lo, t_hi) in it["sub"]:
+                assert t_lo == t_hi if r0 >= M else True
+        for (sp, r0, tiles) in walks:
             if r0 >= M:
-                assert t_lo == t_hi
                 continue
             rows = torch.arange(r0, r0 + TILE)
             m_run = torch.full((TILE,), float("-inf"))
             l_run = torch.zeros(TILE)
-            for t in range(t_lo, t_hi):
+            for t in tiles:
                 assert it["chunk"][0] <= t < it["chunk"][1]
                 visits[1].append((bh, r0, t))
                 c0 = t * TILE
@@ -77,14 +85,20 @@ def emulate(q: torch.Tensor, k: torch.Tensor, reduction: str, is_causal: bool, s
     for item in range(pl.col_items):
         it = nat.plan_item(prob, pl, 2, item)
         bh, sp = it["head"], it["split"]
-        for (r0, t_lo, t_hi) in it["sub"]:
+        if pl.key_stream:
+            # key streaming: every key tile of the chunk against the head's single query tile
+            sp = 0
+            subs = [(kt * TILE, 0, 1) for kt in range(*it["chunk"])]
+        else:
+            subs = it["sub"]
+        for (r0, t_lo, t_hi) in subs:
             if r0 >= N:
                 assert t_lo == t_hi
                 continue
             keys = torch.arange(r0, r0 + TILE)
             acc = torch.full((TILE,), float("-inf")) if is_max else torch.zeros(TILE)
             for t in range(t_lo, t_hi):
-                assert it["chunk"][0] <= t < it["chunk"][1]
+                assert pl.key_stream or it["chunk"][0] <= t < it["chunk"][1]
                 visits[2].append((bh, r0, t))
                 c0 = t * TILE
                 s = sign * (kpad[bh, r0:r0 + TILE] @ qpad[bh, c0:c0 + TILE].T)  # (keys, queries)

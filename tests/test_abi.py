@@ -48,8 +48,13 @@ def test_plan_counts_valid_scores(cfg, scores):
     assert pl.valid_scores == scores
     assert pl.d_pad == (64 if d <= 64 else 128 if d <= 128 else 256)
     assert pl.m_pad % 128 == 0 and pl.m_pad >= m and pl.n_pad % 128 == 0 and pl.n_pad >= n
-    assert pl.row_items == b * h * pl.row_blocks * pl.row_splits
-    assert pl.col_items == b * h * pl.col_blocks * pl.col_splits
+    if pl.key_stream:  # decode shape: key chunks are the work items of both passes
+        assert (m, n) == (128, 4096) and pl.key_chunks >= 1
+        assert pl.row_items == pl.col_items == b * h * pl.key_chunks
+        assert pl.row_splits == 4 * pl.key_chunks and pl.col_splits == 1
+    else:
+        assert pl.row_items == b * h * pl.row_blocks * pl.row_splits
+        assert pl.col_items == b * h * pl.col_blocks * pl.col_splits
     assert 1 <= pl.row_ctas <= 148 and 1 <= pl.col_ctas <= 148
     assert pl.workspace_bytes >= 256 + b * h * pl.m_pad * 4
     assert nat.lib.fcr_workspace_bytes(C.byref(_problem(b, h, m, n, d, causal=causal)), 148) == pl.workspace_bytes

@@ -190,6 +190,39 @@ def test_many_items_per_cta_with_a_skipped_half_block(d):
             assert_parity(_f32(q.to(dev), k.to(dev), red, causal), oracle_colreduce(q, k, red, causal), red)
 
 
+@pytest.mark.parametrize("b,h,m,n,d", [(1, 2, 1, 1024, 128), (2, 3, 7, 1500, 64), (1, 4, 64, 4099, 128),
+                                       (1, 2, 100, 2048, 72), (1, 1, 128, 8192, 128), (3, 50, 33, 1027, 64),
+                                       (1, 160, 128, 1024, 128)])
+def test_decode_shapes_stream_the_keys(b, h, m, n, d):
+    """M <= 128 with at least 8 key tiles: the key-streaming kernels (one query tile per head kept in
+    shared memory, several work items and heads per CTA in the last two cases)."""
+    from flash_colreduce_b200 import _native as nat
+
+    dev = _dev()
+    q, k = _rand((b, h, m, d), 50), _rand((b, h, n, d), 51)
+    pr = nat.make_problem(b, h, m, n, d, q.stride(), k.stride(), nat.FCR_F16, 0, True, 0.1)
+    assert nat.plan(pr, 148).key_stream == 1
+    for red in ("sum", "mean", "max"):
+        for causal in (False, True):
+            assert_parity(_f32(q.to(dev), k.to(dev), red, causal), oracle_colreduce(q, k, red, causal), red)
+
+
+def test_decode_shapes_other_dtypes():
+    from flash_colreduce_b200 import flash_colreduce
+
+    dev = _dev()
+    q, k = _rand((2, 2, 40, 64), 52, torch.bfloat16), _rand((2, 2, 3000, 64), 53, torch.bfloat16)
+    for red in ("sum", "max"):
+        got = flash_colreduce(q.to(dev), k.to(dev), red, is_causal=True)
+        assert_parity(got, oracle_colreduce(q, k, red, True), red, extra_rtol=8e-3)
+    q = _tf32(_rand((1, 3, 20, 48), 54, torch.float32))
+    k = _tf32(_rand((1, 3, 2500, 48), 55, torch.float32))
+    for red in ("sum", "mean", "max"):
+        for causal in (False, True):
+            got = flash_colreduce(q.to(dev), k.to(dev), red, is_causal=causal)
+            assert_parity(got, oracle_colreduce(q, k, red, causal), red)
+
+
 def test_zero_scale_gives_uniform_rows():
     dev = _dev()
     q, k = _rand((1, 2, 100, 64), 32), _rand((1, 2, 300, 64), 33)

@@ -12,7 +12,8 @@ import torch
 from emulate import TILE, emulate
 from oracle import oracle_colreduce
 
-SHAPES = [(128, 128), (131, 131), (128, 1024), (131, 1027), (300, 100), (1, 500), (700, 700), (513, 257), (257, 513)]
+SHAPES = [(128, 128), (131, 131), (128, 1024), (131, 1027), (300, 100), (1, 500), (700, 700), (513, 257), (257, 513),
+          (1, 1500), (100, 1027), (128, 4096)]
 
 
 def _needed_tiles(m, n, causal, off):
