@@ -250,10 +250,17 @@ keystream_kernel(const __grid_constant__ CUtensorMap tmap_q,
         const int valid_hi = p.causal ? (int)hd_min((long long)p.N, (long long)mine + p.off + 1) : p.N;
         int mask_from = p.N >> 7;
         if (p.causal) mask_from = (int)hd_min((long long)mask_from, ((long long)p.off + 1) >> 7);
+        // a warp whose 32 lanes all lie beyond the last query has nothing to fold
+        const bool live = (warp & 3) * 32 < p.M;
         for (int t = t_lo + wg; t < t_hi; t += kKsBuffers) {
           ok = WAIT(bar_tm_full(wg), my_use & 1u, ST_KS_WAIT_TMEM_FULL);
           if (!ok) break;
           ++my_use;
+          if (!live) {
+            if (lane == 0) ptx::mbar_arrive(bar_tm_empty(wg));
+            __syncwarp();
+            continue;
+          }
           ptx::tc_fence_after_sync();
           const bool need_mask = t >= mask_from;
           const int lim_hi = valid_hi - t * kTile;
