@@ -749,6 +749,7 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
 
 }  // namespace fcr
 #include "keystream_sm100.cuh"
+#include "topk.cuh"
 namespace fcr {
 
 // Combines the per-split running (max, sum) of the rows pass into -lse.
@@ -1047,6 +1048,20 @@ static void fill_mean(PassParams& pp, int reduction, int is_causal, int M, int N
   pp.div_N = N;
   pp.div_c = N > M ? N - M : 0;
   pp.mean_mode = reduction == FCR_MEAN ? (is_causal ? 2 : 1) : 0;
+}
+
+template <typename T>
+static int launch_topk(const void* scores, int rows, int n, int k, void* indices, int index_bits,
+                       void* values, cudaStream_t stream) {
+  if (index_bits == 64)
+    topk_kernel<T, long long><<<rows, kTopkThreads, 0, stream>>>(
+        static_cast<const T*>(scores), n, k, static_cast<long long*>(indices), static_cast<T*>(values));
+  else
+    topk_kernel<T, int><<<rows, kTopkThreads, 0, stream>>>(
+        static_cast<const T*>(scores), n, k, static_cast<int*>(indices), static_cast<T*>(values));
+  const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "topk launch");
+  return FCR_OK;
 }
 
 }  // namespace fcr
@@ -1367,6 +1382,22 @@ int fcr_colreduce_static(const fcr_problem* problem, const void* q, const void* 
   // and scheduler counters at its start are cleared on the stream by that call;
   // everything else in the array is written before it is read.
   return fcr_colreduce(problem, q, k, out, out_dtype, scratch, kStaticScratchBytes, stream_v);
+}
+
+int fcr_topk(const void* scores, int32_t dtype, int32_t rows, int32_t n, int32_t k, void* indices,
+             int32_t index_bits, void* values, void* stream_v) {
+  if (!scores || !indices) return fail(FCR_ERR_BAD_ARG, "null scores or indices");
+  if (rows <= 0 || n <= 0) return fail(FCR_ERR_BAD_ARG, "rows and n must be positive");
+  if (k < 1 || k > n)
+    return fail(FCR_ERR_BAD_ARG, "k = " + std::to_string(k) + " must lie in [1, n = " + std::to_string(n) + "]");
+  if (index_bits != 32 && index_bits != 64) return fail(FCR_ERR_BAD_ARG, "index_bits must be 32 or 64");
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
+  switch (dtype) {
+    case FCR_F16: return launch_topk<__half>(scores, rows, n, k, indices, index_bits, values, stream);
+    case FCR_BF16: return launch_topk<__nv_bfloat16>(scores, rows, n, k, indices, index_bits, values, stream);
+    case FCR_F32: return launch_topk<float>(scores, rows, n, k, indices, index_bits, values, stream);
+    default: return fail(FCR_ERR_BAD_ARG, "invalid dtype");
+  }
 }
 
 double fcr_probe_ex2_rate(int32_t repeats) {

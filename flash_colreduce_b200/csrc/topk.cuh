@@ -1,0 +1,200 @@
+// Row-wise top-k selection over the (B*H, N) score array the column reduction
+// produces: the step a token-pruning consumer runs next (the reference's
+// README.md:9 names that use; the reference itself stops at the scores, so this
+// kernel has no counterpart there).
+//
+// One CTA per row.  The k-th largest value is found by a most-significant-byte
+// first radix select on an order-preserving key (four histogram rounds for fp32
+// scores, two for fp16 / bf16, each a sweep over the row, which stays in the L2
+// cache; one histogram per lane, so skewed scores cause no shared-memory
+// conflicts), then one more sweep compacts the selected positions in ascending
+// index order with a block-wide scan: every element above the threshold, plus
+// the first `ties` elements equal to it.  Deterministic; a NaN with a clear sign
+// bit (the 0/0 of an empty mean) orders above +inf, as in torch.topk.
+//
+// Included by colreduce_sm100.cu (needs FCR_F16 / FCR_BF16 / FCR_F32).
+#pragma once
+
+namespace fcr {
+
+constexpr int kTopkThreads = 1024;
+constexpr int kTopkItems = 8;  // consecutive elements per thread and sweep step (one 16-byte load for 16-bit scores)
+
+// Order-preserving unsigned key of a score: 32 bits for fp32, 16 bits for fp16 / bf16 (both are
+// sign-magnitude formats, so the same bit trick orders them), hence two radix rounds instead of four.
+template <typename T>
+struct TopkKey;
+template <>
+struct TopkKey<float> {
+  static constexpr int kBits = 32;
+  static __device__ __forceinline__ uint32_t of(float x) {
+    const uint32_t u = __float_as_uint(x);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+  }
+};
+template <>
+struct TopkKey<__half> {
+  static constexpr int kBits = 16;
+  static __device__ __forceinline__ uint32_t of(__half x) {
+    const uint32_t u = __half_as_ushort(x);
+    return (u & 0x8000u) ? (~u & 0xffffu) : (u | 0x8000u);
+  }
+};
+template <>
+struct TopkKey<__nv_bfloat16> {
+  static constexpr int kBits = 16;
+  static __device__ __forceinline__ uint32_t of(__nv_bfloat16 x) {
+    const uint32_t u = __bfloat16_as_ushort(x);
+    return (u & 0x8000u) ? (~u & 0xffffu) : (u | 0x8000u);
+  }
+};
+
+// Keys of elements [i0, i0 + 8) of a row (unspecified beyond n); 16-byte loads when the address allows.
+template <typename T>
+__device__ __forceinline__ void topk_load8(const T* row, int i0, int n, uint32_t (&key)[kTopkItems]) {
+  const T* p = row + i0;
+  if (i0 + kTopkItems <= n && (reinterpret_cast<uintptr_t>(p) & 15u) == 0) {
+    constexpr int kVecs = (int)(kTopkItems * sizeof(T) / 16);
+    uint4 raw[kVecs];
+#pragma unroll
+    for (int v = 0; v < kVecs; ++v) raw[v] = reinterpret_cast<const uint4*>(p)[v];
+    const T* e = reinterpret_cast<const T*>(raw);
+#pragma unroll
+    for (int j = 0; j < kTopkItems; ++j) key[j] = TopkKey<T>::of(e[j]);
+  } else {
+#pragma unroll
+    for (int j = 0; j < kTopkItems; ++j) key[j] = (i0 + j < n) ? TopkKey<T>::of(p[j]) : 0u;
+  }
+}
+
+template <typename T, typename IndexT>
+__global__ void __launch_bounds__(kTopkThreads)
+topk_kernel(const T* __restrict__ scores, int n, int k, IndexT* __restrict__ indices,
+            T* __restrict__ values) {
+  // One histogram per lane: hist[bin * 32 + lane].  A warp's 32 adds then touch 32 different
+  // banks and never the same word, however skewed the scores are.
+  __shared__ int hist[256 * 32];
+  __shared__ uint32_t s_prefix, s_want;
+  __shared__ uint32_t warp_tot[kTopkThreads / 32];
+  __shared__ uint32_t chunk_tot;
+  const T* row = scores + (size_t)blockIdx.x * n;
+  IndexT* out_idx = indices + (size_t)blockIdx.x * k;
+  T* out_val = values ? values + (size_t)blockIdx.x * k : nullptr;
+  const int tid = (int)threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  constexpr int kStep = kTopkThreads * kTopkItems;
+
+  // ---- radix select: after the last round `prefix` is the key of the k-th largest element
+  uint32_t prefix = 0, mask = 0, want = (uint32_t)k;
+  for (int shift = TopkKey<T>::kBits - 8; shift >= 0; shift -= 8) {
+#pragma unroll
+    for (int j = 0; j < 256 * 32 / kTopkThreads; ++j) hist[j * kTopkThreads + tid] = 0;
+    __syncthreads();
+    for (int c0 = 0; c0 < n; c0 += kStep) {
+      const int i0 = c0 + tid * kTopkItems;
+      uint32_t key[kTopkItems];
+      topk_load8<T>(row, i0, n, key);
+#pragma unroll
+      for (int j = 0; j < kTopkItems; ++j) {
+        if (i0 + j < n && (key[j] & mask) == prefix)
+          atomicAdd(&hist[((key[j] >> shift) & 255u) * 32 + lane], 1);
+      }
+    }
+    __syncthreads();
+    // bin totals (thread b sums the 32 copies of bin b, starting at its own lane: no bank conflicts)
+    int total = 0;
+    if (tid < 256) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) total += hist[tid * 32 + ((j + lane) & 31)];
+    }
+    __syncthreads();
+    if (tid < 256) hist[tid] = total;
+    __syncthreads();
+    if (warp == 0) {
+      // lane L owns bins [8L, 8L + 8); `above` = elements in higher bins
+      uint32_t mine = 0;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) mine += (uint32_t)hist[lane * 8 + j];
+      uint32_t suffix = mine;  // inclusive sum over lanes >= L
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const uint32_t dn = __shfl_down_sync(0xffffffffu, suffix, d);
+        if (lane + d < 32) suffix += dn;
+      }
+      uint32_t above = suffix - mine;
+      if (above < want && want <= suffix) {  // the wanted element lies in one of this lane's bins
+        int b = lane * 8 + 7;
+        for (; b > lane * 8; --b) {
+          if (above + (uint32_t)hist[b] >= want) break;
+          above += (uint32_t)hist[b];
+        }
+        s_prefix = prefix | ((uint32_t)b << shift);
+        s_want = want - above;  // how many elements of bin b are still needed
+      }
+    }
+    __syncthreads();
+    prefix = s_prefix;
+    want = s_want;
+    mask |= 255u << shift;
+    __syncthreads();
+  }
+  const uint32_t thr = prefix;  // key of the k-th largest element
+  const uint32_t ties = want;   // elements equal to it that are selected (the first ones by index)
+
+  // ---- compaction in ascending index order
+  uint32_t gt_base = 0, eq_base = 0;
+  for (int c0 = 0; c0 < n; c0 += kStep) {
+    const int i0 = c0 + tid * kTopkItems;
+    uint32_t key[kTopkItems];
+    topk_load8<T>(row, i0, n, key);
+    uint32_t g = 0, e = 0;
+    bool isg[kTopkItems], ise[kTopkItems];
+#pragma unroll
+    for (int j = 0; j < kTopkItems; ++j) {
+      isg[j] = i0 + j < n && key[j] > thr;
+      ise[j] = i0 + j < n && key[j] == thr;
+      g += isg[j];
+      e += ise[j];
+    }
+    // block-wide exclusive scan of (g, e), packed into 16-bit halves (a step holds 8192 elements)
+    const uint32_t v = g | (e << 16);
+    uint32_t incl = v;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const uint32_t up = __shfl_up_sync(0xffffffffu, incl, d);
+      if (lane >= d) incl += up;
+    }
+    if (lane == 31) warp_tot[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+      const uint32_t w = warp_tot[lane];
+      uint32_t wi = w;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const uint32_t up = __shfl_up_sync(0xffffffffu, wi, d);
+        if (lane >= d) wi += up;
+      }
+      warp_tot[lane] = wi - w;  // exclusive
+      if (lane == 31) chunk_tot = wi;
+    }
+    __syncthreads();
+    const uint32_t excl = warp_tot[warp] + (incl - v);
+    uint32_t g_before = gt_base + (excl & 0xffffu);
+    uint32_t e_before = eq_base + (excl >> 16);
+#pragma unroll
+    for (int j = 0; j < kTopkItems; ++j) {
+      if (isg[j] || (ise[j] && e_before < ties)) {
+        const uint32_t pos = g_before + min(e_before, ties);
+        out_idx[pos] = (IndexT)(i0 + j);
+        if (out_val) out_val[pos] = row[i0 + j];
+      }
+      g_before += isg[j];
+      e_before += ise[j];
+    }
+    const uint32_t tot = chunk_tot;
+    gt_base += tot & 0xffffu;
+    eq_base += tot >> 16;
+    __syncthreads();  // warp_tot / chunk_tot are rewritten by the next step
+  }
+}
+
+}  // namespace fcr

@@ -16,7 +16,8 @@ import torch
 
 from . import _native as nat
 
-__all__ = ["flash_colreduce", "colreduce_partial", "finalize_scores", "valid_scores"]
+__all__ = ["flash_colreduce", "colreduce_partial", "finalize_scores", "valid_scores", "topk_columns",
+           "flash_colreduce_topk"]
 
 _DTYPE_CODES = {torch.float16: nat.FCR_F16, torch.bfloat16: nat.FCR_BF16, torch.float32: nat.FCR_F32}
 
@@ -190,6 +191,40 @@ def finalize_scores(acc: torch.Tensor, m: int, reduction: str, is_causal: bool, 
                                   nat.REDUCTION_CODES[reduction], 1 if is_causal else 0, stream)
         nat.check(rc, "fcr_finalize")
     return out
+
+
+def topk_columns(scores: torch.Tensor, k: int, return_values: bool = True):
+    """The ``k`` highest-scoring key positions of every (batch, head) row of ``scores`` (..., N).
+
+    Returns ``(values, indices)`` like ``torch.topk`` (``values`` is ``None`` when not asked for), but
+    in ascending position order -- the order a token-pruning consumer gathers in -- and with ties at
+    the k-th score resolved towards the lowest positions.  One kernel launch on the current stream.
+    The reference stops at the scores (its README.md:9 names this use); there is no counterpart.
+    """
+    if not scores.is_cuda:
+        raise ValueError("scores must be on a CUDA device.")
+    if scores.dtype not in _DTYPE_CODES:
+        raise TypeError(f"topk_columns takes fp16, bf16 or fp32 scores; got {scores.dtype}.")
+    n = scores.shape[-1]
+    if not 1 <= k <= n:
+        raise ValueError(f"k = {k} must lie in [1, {n}].")
+    flat = scores.contiguous().view(-1, n)
+    lead = scores.shape[:-1]
+    indices = torch.empty((flat.shape[0], k), dtype=torch.int64, device=scores.device)
+    values = torch.empty((flat.shape[0], k), dtype=scores.dtype, device=scores.device) if return_values else None
+    if flat.shape[0] > 0:
+        with torch.cuda.device(scores.device):
+            stream = torch.cuda.current_stream(scores.device).cuda_stream
+            rc = nat.lib.fcr_topk(flat.data_ptr(), _DTYPE_CODES[scores.dtype], flat.shape[0], n, k,
+                                  indices.data_ptr(), 64, values.data_ptr() if return_values else None, stream)
+            nat.check(rc, "fcr_topk")
+    return (values.view(*lead, k) if return_values else None), indices.view(*lead, k)
+
+
+def flash_colreduce_topk(query: torch.Tensor, key: torch.Tensor, reduction: str, k: int, is_causal: bool = False,
+                         scale: Optional[float] = None):
+    """``flash_colreduce`` followed by :func:`topk_columns`: ``(values, indices)`` of shape (B, H, k)."""
+    return topk_columns(flash_colreduce(query, key, reduction, is_causal=is_causal, scale=scale), k)
 
 
 def valid_scores(b: int, h: int, m: int, n: int, is_causal: bool) -> int:

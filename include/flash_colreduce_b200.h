@@ -232,6 +232,21 @@ int fcr_debug_scores(const fcr_problem* problem, const void* q, const void* k, f
                      void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * Row-wise top-k over a contiguous (rows, n) score array of dtype `dtype`
+ * (FCR_F16, FCR_BF16 or FCR_F32), e.g. the (B*H, N) output of fcr_colreduce:
+ * for every row the positions of its k largest scores, in ascending position
+ * order, as int32 (index_bits = 32) or int64 (index_bits = 64) into
+ * `indices` (rows, k), and, when `values` is not null, the scores at those
+ * positions into `values` (rows, k) of the same dtype.  Among scores equal to
+ * the k-th largest the lowest positions win; NaN orders above +inf.  This is
+ * the selection step of the token-pruning use the reference's README.md:9
+ * names; the reference has no counterpart (it returns the scores).  One
+ * launch on `stream`, no workspace, no allocation, no host synchronisation.
+ */
+int fcr_topk(const void* scores, int32_t dtype, int32_t rows, int32_t n, int32_t k, void* indices,
+             int32_t index_bits, void* values, void* stream);
+
+/*
  * Measurement helper: runs a register-only ex2.approx.ftz.f32 loop on every
  * SM and returns the sustained rate in exponentials per second (the MUFU
  * bound of the roofline).  Synchronises the device.  Returns 0 on error.

@@ -1,0 +1,73 @@
+"""Top-k selection over the column scores (fcr_topk), against torch.topk on the CPU."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _dev():
+    return torch.device("cuda", 0)
+
+
+def _check(scores_cpu: torch.Tensor, k: int):
+    from flash_colreduce_b200 import topk_columns
+
+    vals, idx = topk_columns(scores_cpu.to(_dev()), k)
+    vals, idx = vals.cpu(), idx.cpu()
+    assert idx.shape == scores_cpu.shape[:-1] + (k,) and idx.dtype == torch.int64
+    # positions ascending and distinct, values are the scores at those positions
+    assert (idx[..., 1:] > idx[..., :-1]).all()
+    assert torch.equal(vals, torch.gather(scores_cpu, -1, idx))
+    # the same multiset of values as torch.topk ...
+    want_vals, _ = torch.topk(scores_cpu.float(), k, dim=-1)
+    got_sorted = vals.float().sort(dim=-1, descending=True)[0]
+    assert torch.equal(got_sorted, want_vals)
+    # ... and among the scores equal to the k-th largest, the lowest positions
+    flat, fidx = scores_cpu.float().reshape(-1, scores_cpu.shape[-1]), idx.reshape(-1, k)
+    for r in range(min(flat.shape[0], 16)):
+        thr = want_vals.reshape(-1, k)[r, -1]
+        want = torch.cat([(flat[r] > thr).nonzero().flatten(),
+                          (flat[r] == thr).nonzero().flatten()[: k - int((flat[r] > thr).sum())]]).sort()[0]
+        assert torch.equal(fidx[r], want)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("rows,n,k", [(1, 1, 1), (3, 100, 7), (5, 4096, 4096), (2, 5000, 1), (4, 70001, 2500),
+                                      (300, 1027, 257)])
+def test_matches_torch_topk(dtype, rows, n, k):
+    g = torch.Generator().manual_seed(rows * 31 + n + k)
+    _check(torch.rand(rows, n, generator=g).to(dtype), k)  # 16-bit dtypes: many exact ties
+
+
+def test_ties_negative_values_and_infinities():
+    s = torch.zeros(2, 3, 1000)
+    _check(s, 10)  # all equal: the first ten positions
+    s = -torch.rand(2, 3, 1000, generator=torch.Generator().manual_seed(1))
+    s[0, 0, 5] = float("inf")
+    s[0, 1, 7] = float("-inf")
+    s[1, 2, 999] = 0.0
+    _check(s, 3)
+    _check(s, 999)
+
+
+def test_on_the_scores_of_the_operator_and_argument_checks():
+    from flash_colreduce_b200 import flash_colreduce, flash_colreduce_topk, topk_columns
+
+    dev = _dev()
+    g = torch.Generator().manual_seed(3)
+    q = torch.randn(2, 4, 200, 64, generator=g).half().to(dev)
+    k = torch.randn(2, 4, 700, 64, generator=g).half().to(dev)
+    vals, idx = flash_colreduce_topk(q, k, "mean", 50, is_causal=True)
+    scores = flash_colreduce(q, k, "mean", is_causal=True)
+    assert idx.shape == (2, 4, 50) and torch.equal(vals, torch.gather(scores, -1, idx))
+    _check(scores.cpu(), 50)
+    none_vals, idx2 = topk_columns(scores, 50, return_values=False)
+    assert none_vals is None and torch.equal(idx2, idx)
+    with pytest.raises(ValueError, match="must lie in"):
+        topk_columns(scores, 0)
+    with pytest.raises(ValueError, match="must lie in"):
+        topk_columns(scores, 701)
+    with pytest.raises(TypeError):
+        topk_columns(scores.double(), 3)
+    with pytest.raises(ValueError, match="CUDA"):
+        topk_columns(scores.cpu(), 3)
