@@ -207,6 +207,28 @@ def test_decode_shapes_stream_the_keys(b, h, m, n, d):
             assert_parity(_f32(q.to(dev), k.to(dev), red, causal), oracle_colreduce(q, k, red, causal), red)
 
 
+def test_decode_full_size_properties():
+    """A decode batch too large for the oracle (2 GiB of keys): every query row's softmax sums to one, so
+    the columns of a head sum to M; max lies in (0, 1]; two runs agree bit for bit."""
+    from flash_colreduce_b200 import flash_colreduce
+
+    dev = _dev()
+    g = torch.Generator(device=dev).manual_seed(7)
+    b, h, m, n, d = 8, 32, 16, 32768, 128
+    q = torch.randn(b, h, m, d, generator=g, device=dev, dtype=torch.float16)
+    k = torch.randn(b, h, n, d, generator=g, device=dev, dtype=torch.float16)
+    for causal in (False, True):
+        s1 = flash_colreduce(q.float().half(), k, "sum", is_causal=causal).float()
+        total = s1.sum(dim=-1)
+        assert torch.allclose(total, torch.full_like(total, float(m)), rtol=2e-3)
+        assert torch.equal(flash_colreduce(q, k, "sum", is_causal=causal).float(), s1)
+        mx = flash_colreduce(q, k, "max", is_causal=causal).float()
+        assert (mx > 0).all() and (mx <= 1.0 + 1e-3).all()
+        # a column's mean over the queries that see it cannot exceed its max
+        mean = flash_colreduce(q, k, "mean", is_causal=causal).float()
+        assert (mean <= mx * (1 + 2e-3) + 1e-6).all()
+
+
 def test_decode_shapes_other_dtypes():
     from flash_colreduce_b200 import flash_colreduce
 
