@@ -1050,18 +1050,45 @@ static void fill_mean(PassParams& pp, int reduction, int is_causal, int M, int N
   pp.mean_mode = reduction == FCR_MEAN ? (is_causal ? 2 : 1) : 0;
 }
 
+// CTAs per row: one when the rows alone fill the GPU, else a cluster of 2, 4 or 8 that splits the
+// row, as long as every CTA keeps at least one full sweep step (8192 elements).
+static int topk_cluster_size(int rows, int n, int sms) {
+  int c = 1;
+  while (c < 8 && (long long)rows * c * 2 <= sms && n / (c * 2) >= kTopkThreads * kTopkItems) c *= 2;
+  return c;
+}
+
+template <typename T, typename IndexT>
+static int launch_topk_t(const void* scores, int rows, int n, int k, void* indices, void* values,
+                         int cluster, cudaStream_t stream) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)rows * cluster);
+  cfg.blockDim = dim3(kTopkThreads);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = (unsigned)cluster;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = cluster > 1 ? 1 : 0;  // a single CTA per row is an ordinary launch
+  cudaError_t e = cudaLaunchKernelEx(&cfg, topk_kernel<T, IndexT>, static_cast<const T*>(scores), n, k,
+                                     static_cast<IndexT*>(indices), static_cast<T*>(values));
+  if (e == cudaSuccess) e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "topk launch");
+  return FCR_OK;
+}
+
 template <typename T>
 static int launch_topk(const void* scores, int rows, int n, int k, void* indices, int index_bits,
                        void* values, cudaStream_t stream) {
+  int sms = 0;
+  const int rc = device_sm_count(&sms);
+  if (rc != FCR_OK) return rc;
+  const int cluster = topk_cluster_size(rows, n, sms);
   if (index_bits == 64)
-    topk_kernel<T, long long><<<rows, kTopkThreads, 0, stream>>>(
-        static_cast<const T*>(scores), n, k, static_cast<long long*>(indices), static_cast<T*>(values));
-  else
-    topk_kernel<T, int><<<rows, kTopkThreads, 0, stream>>>(
-        static_cast<const T*>(scores), n, k, static_cast<int*>(indices), static_cast<T*>(values));
-  const cudaError_t e = cudaGetLastError();
-  if (e != cudaSuccess) return cuda_fail(e, "topk launch");
-  return FCR_OK;
+    return launch_topk_t<T, long long>(scores, rows, n, k, indices, values, cluster, stream);
+  return launch_topk_t<T, int>(scores, rows, n, k, indices, values, cluster, stream);
 }
 
 }  // namespace fcr

@@ -3,7 +3,11 @@
 // README.md:9 names that use; the reference itself stops at the scores, so this
 // kernel has no counterpart there).
 //
-// One CTA per row.  The k-th largest value is found by a most-significant-byte
+// One thread-block cluster per row: a single CTA when there are enough rows to
+// fill the GPU, otherwise 2, 4 or 8 CTAs that each own a contiguous slice of the
+// row and exchange their 256-bin histograms and their selected-element counts
+// through distributed shared memory (cluster.sync() is a hardware barrier, there
+// is no spin wait).  The k-th largest value is found by a most-significant-byte
 // first radix select on an order-preserving key (four histogram rounds for fp32
 // scores, two for fp16 / bf16, each a sweep over the row, which stays in the L2
 // cache; one histogram per lane, so skewed scores cause no shared-memory
@@ -14,6 +18,7 @@
 //
 // Included by colreduce_sm100.cu (needs FCR_F16 / FCR_BF16 / FCR_F32).
 #pragma once
+#include <cooperative_groups.h>
 
 namespace fcr {
 
@@ -71,17 +76,26 @@ template <typename T, typename IndexT>
 __global__ void __launch_bounds__(kTopkThreads)
 topk_kernel(const T* __restrict__ scores, int n, int k, IndexT* __restrict__ indices,
             T* __restrict__ values) {
+  namespace cg = cooperative_groups;
+  cg::cluster_group cluster = cg::this_cluster();
+  const int n_ranks = (int)cluster.num_blocks(), rank = (int)cluster.block_rank();
   // One histogram per lane: hist[bin * 32 + lane].  A warp's 32 adds then touch 32 different
   // banks and never the same word, however skewed the scores are.
   __shared__ int hist[256 * 32];
+  __shared__ int bin_total[256];     // this CTA's slice, read by the other CTAs of the cluster
+  __shared__ uint32_t slice_cnt[2];  // elements above / equal to the threshold in this CTA's slice
   __shared__ uint32_t s_prefix, s_want;
   __shared__ uint32_t warp_tot[kTopkThreads / 32];
   __shared__ uint32_t chunk_tot;
-  const T* row = scores + (size_t)blockIdx.x * n;
-  IndexT* out_idx = indices + (size_t)blockIdx.x * k;
-  T* out_val = values ? values + (size_t)blockIdx.x * k : nullptr;
+  const size_t row_id = blockIdx.x / n_ranks;
+  const T* row = scores + row_id * n;
+  IndexT* out_idx = indices + row_id * k;
+  T* out_val = values ? values + row_id * k : nullptr;
   const int tid = (int)threadIdx.x, lane = tid & 31, warp = tid >> 5;
   constexpr int kStep = kTopkThreads * kTopkItems;
+  // this CTA's slice [lo, hi) of the row; inner boundaries are multiples of 8 elements
+  const int lo = (int)(((long long)n * rank / n_ranks) & ~7LL);
+  const int hi = rank + 1 == n_ranks ? n : (int)(((long long)n * (rank + 1) / n_ranks) & ~7LL);
 
   // ---- radix select: after the last round `prefix` is the key of the k-th largest element
   uint32_t prefix = 0, mask = 0, want = (uint32_t)k;
@@ -89,31 +103,38 @@ topk_kernel(const T* __restrict__ scores, int n, int k, IndexT* __restrict__ ind
 #pragma unroll
     for (int j = 0; j < 256 * 32 / kTopkThreads; ++j) hist[j * kTopkThreads + tid] = 0;
     __syncthreads();
-    for (int c0 = 0; c0 < n; c0 += kStep) {
+    for (int c0 = lo; c0 < hi; c0 += kStep) {
       const int i0 = c0 + tid * kTopkItems;
       uint32_t key[kTopkItems];
-      topk_load8<T>(row, i0, n, key);
+      topk_load8<T>(row, i0, hi, key);
 #pragma unroll
       for (int j = 0; j < kTopkItems; ++j) {
-        if (i0 + j < n && (key[j] & mask) == prefix)
+        if (i0 + j < hi && (key[j] & mask) == prefix)
           atomicAdd(&hist[((key[j] >> shift) & 255u) * 32 + lane], 1);
       }
     }
     __syncthreads();
     // bin totals (thread b sums the 32 copies of bin b, starting at its own lane: no bank conflicts)
-    int total = 0;
     if (tid < 256) {
+      int total = 0;
 #pragma unroll
       for (int j = 0; j < 32; ++j) total += hist[tid * 32 + ((j + lane) & 31)];
+      bin_total[tid] = total;
     }
-    __syncthreads();
-    if (tid < 256) hist[tid] = total;
-    __syncthreads();
+    cluster.sync();  // every slice's totals are complete (also a barrier of this CTA)
     if (warp == 0) {
-      // lane L owns bins [8L, 8L + 8); `above` = elements in higher bins
+      // lane L owns bins [8L, 8L + 8), summed over the slices; `above` = elements in higher bins
+      uint32_t bins[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) bins[j] = 0;
+      for (int r = 0; r < n_ranks; ++r) {
+        const int* remote = cluster.map_shared_rank(bin_total, r);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) bins[j] += (uint32_t)remote[lane * 8 + j];
+      }
       uint32_t mine = 0;
 #pragma unroll
-      for (int j = 0; j < 8; ++j) mine += (uint32_t)hist[lane * 8 + j];
+      for (int j = 0; j < 8; ++j) mine += bins[j];
       uint32_t suffix = mine;  // inclusive sum over lanes >= L
 #pragma unroll
       for (int d = 1; d < 32; d <<= 1) {
@@ -122,36 +143,67 @@ topk_kernel(const T* __restrict__ scores, int n, int k, IndexT* __restrict__ ind
       }
       uint32_t above = suffix - mine;
       if (above < want && want <= suffix) {  // the wanted element lies in one of this lane's bins
-        int b = lane * 8 + 7;
-        for (; b > lane * 8; --b) {
-          if (above + (uint32_t)hist[b] >= want) break;
-          above += (uint32_t)hist[b];
+        int j = 7;
+#pragma unroll
+        for (int u = 7; u > 0; --u) {
+          if (j == u && above + bins[u] < want) {
+            above += bins[u];
+            j = u - 1;
+          }
         }
-        s_prefix = prefix | ((uint32_t)b << shift);
-        s_want = want - above;  // how many elements of bin b are still needed
+        s_prefix = prefix | ((uint32_t)(lane * 8 + j) << shift);
+        s_want = want - above;  // how many elements of that bin are still needed
       }
     }
-    __syncthreads();
+    cluster.sync();  // the totals have been read everywhere: they may be rebuilt in the next round
     prefix = s_prefix;
     want = s_want;
     mask |= 255u << shift;
-    __syncthreads();
   }
   const uint32_t thr = prefix;  // key of the k-th largest element
   const uint32_t ties = want;   // elements equal to it that are selected (the first ones by index)
 
-  // ---- compaction in ascending index order
+  // ---- elements above / equal to the threshold in the slices before this one
   uint32_t gt_base = 0, eq_base = 0;
-  for (int c0 = 0; c0 < n; c0 += kStep) {
+  if (n_ranks > 1) {
+    if (tid < 2) slice_cnt[tid] = 0;
+    __syncthreads();
+    uint32_t g = 0, e = 0;
+    for (int c0 = lo; c0 < hi; c0 += kStep) {
+      const int i0 = c0 + tid * kTopkItems;
+      uint32_t key[kTopkItems];
+      topk_load8<T>(row, i0, hi, key);
+#pragma unroll
+      for (int j = 0; j < kTopkItems; ++j) {
+        g += (i0 + j < hi && key[j] > thr) ? 1u : 0u;
+        e += (i0 + j < hi && key[j] == thr) ? 1u : 0u;
+      }
+    }
+    g = __reduce_add_sync(0xffffffffu, g);
+    e = __reduce_add_sync(0xffffffffu, e);
+    if (lane == 0) {
+      atomicAdd(&slice_cnt[0], g);
+      atomicAdd(&slice_cnt[1], e);
+    }
+    cluster.sync();
+    for (int r = 0; r < rank; ++r) {
+      const uint32_t* remote = cluster.map_shared_rank(slice_cnt, r);
+      gt_base += remote[0];
+      eq_base += remote[1];
+    }
+  }
+
+  // ---- compaction in ascending index order
+  for (int c0 = lo; c0 < hi; c0 += kStep) {
     const int i0 = c0 + tid * kTopkItems;
     uint32_t key[kTopkItems];
-    topk_load8<T>(row, i0, n, key);
+    topk_load8<T>(row, i0, hi, key);
     uint32_t g = 0, e = 0;
     bool isg[kTopkItems], ise[kTopkItems];
 #pragma unroll
     for (int j = 0; j < kTopkItems; ++j) {
-      isg[j] = i0 + j < n && key[j] > thr;
-      ise[j] = i0 + j < n && key[j] == thr;
+      isg[j] = i0 + j < hi && key[j] > thr;
+      ise[j] = i0 + j < hi && key[j] == thr;
       g += isg[j];
       e += ise[j];
     }
@@ -195,6 +247,7 @@ topk_kernel(const T* __restrict__ scores, int n, int k, IndexT* __restrict__ ind
     eq_base += tot >> 16;
     __syncthreads();  // warp_tot / chunk_tot are rewritten by the next step
   }
+  cluster.sync();  // no CTA leaves while another may still read its shared memory
 }
 
 }  // namespace fcr
