@@ -98,6 +98,7 @@ enum {
   ST_WAIT_DRAIN = 24,
   ST_WAIT_TMEM_FULL = 31,
   ST_WAIT_RING_FULL_SM = 32,
+  ST_WAIT_LSE_EMPTY = 14,
   ST_WAIT_SCHED_EMPTY = 13,
   ST_WAIT_SCHED_FULL = 26,
   ST_WAIT_SCHED_FULL_SM = 38,
@@ -139,14 +140,18 @@ struct SmemLayout {
   static constexpr int KS = DPAD == 256 ? 1 : ((DPAD == 64 || SHORT) ? 2 : 1);  // stationary stages
   static constexpr int KR = DPAD == 256 ? 1 : (DPAD == 64 ? 6 : (SHORT ? 2 : 4));  // streamed ring stages
   static constexpr int kLseBytes = kTile * 4;
+  // The lse values of a streamed query tile (columns pass) travel in a ring of their own, deeper
+  // than the tile ring: the tile slots are then released by the MMAs alone and the loads run
+  // ahead of the folds, which only hold the 512-byte lse slots.
+  static constexpr int KL = KR + 4;  // tiles in the ring + tiles being folded + slack
   static constexpr int off_stat = 0;
   static constexpr int off_ring = off_stat + KS * kSubTiles * kTileBytes;
   static constexpr int off_lse = off_ring + KR * kTileBytes;
-  static constexpr int off_merge = off_lse + KR * kLseBytes;  // float2 [2 slots][kSubTiles][kTile]
+  static constexpr int off_merge = off_lse + KL * kLseBytes;  // float2 [2 slots][kSubTiles][kTile]
   static constexpr int kMergeBytes = (kColSplit > 1) ? 2 * kSubTiles * kTile * 8 : 0;
   static constexpr int off_bars = off_merge + kMergeBytes;
   static constexpr int KI = 4;                   // work items announced ahead of their consumers
-  static constexpr int kNumBars = 2 * KS + 2 * KR + 8 + 8 + 2 * KI;
+  static constexpr int kNumBars = 2 * KS + 2 * KR + 8 + 8 + 2 * KI + 2 * KL;
   static constexpr int off_misc = off_bars + 8 * kNumBars;
   static constexpr int kBytes = off_misc + 16 + 48 * KI;  // + the ring of announced work items
   static constexpr int kDynamicBytes = kBytes;
@@ -262,6 +267,9 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
   constexpr int KI = L::KI;
   auto bar_sched_full = [&](uint32_t i) { return bar0 + 8u * (2 * KS + 2 * KR + 16 + i); };
   auto bar_sched_empty = [&](uint32_t i) { return bar0 + 8u * (2 * KS + 2 * KR + 16 + KI + i); };
+  constexpr int KL = L::KL;
+  auto bar_lse_full = [&](uint32_t i) { return bar0 + 8u * (2 * KS + 2 * KR + 16 + 2 * KI + i); };
+  auto bar_lse_empty = [&](uint32_t i) { return bar0 + 8u * (2 * KS + 2 * KR + 16 + 2 * KI + KL + i); };
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + L::off_misc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::off_misc + 4);
   // Announced work items, decoded once by the TMA warp (12 ints each; head -1 ends the kernel).
@@ -299,7 +307,11 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
     }
     for (int i = 0; i < KR; ++i) {
       ptx::mbar_init(bar_ring_full(i), 1);
-      ptx::mbar_init(bar_ring_empty(i), PHASE != PH_COLS ? kMmaWarps : kMmaWarps + kSoftmaxWarps);
+      ptx::mbar_init(bar_ring_empty(i), kMmaWarps);
+    }
+    for (int i = 0; i < KL; ++i) {
+      ptx::mbar_init(bar_lse_full(i), 1);
+      ptx::mbar_init(bar_lse_empty(i), kSoftmaxWarps);
     }
     for (int a = 0; a < 2; ++a)
       for (int ts = 0; ts < 2; ++ts) {
@@ -413,18 +425,25 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
         ok = WAIT(bar_ring_empty(s), ph ^ 1u, ST_WAIT_RING_EMPTY);
         if (!ok) break;
         if (lane == 0) {
-          ptx::mbar_arrive_expect_tx(bar_ring_full(s),
-                                     L::kTileBytes + (PHASE == PH_COLS ? L::kLseBytes : 0));
+          ptx::mbar_arrive_expect_tx(bar_ring_full(s), L::kTileBytes);
 #pragma unroll
           for (int hf = 0; hf < L::kHalves; ++hf)
             ptx::tma_load_4d(s_ring + s * L::kTileBytes + hf * L::kHalfBytes, &tmap_strm,
                              bar_ring_full(s), hf * p.slab_elems, t * kTile, h, b);
-          if (PHASE == PH_COLS)
-            ptx::bulk_load(s_lse + s * L::kLseBytes,
-                           p.neg_lse + (size_t)g.bh * p.m_pad + (size_t)t * kTile, L::kLseBytes,
-                           bar_ring_full(s));
         }
         __syncwarp();
+        if (PHASE == PH_COLS) {  // the tile's lse values, into their own ring
+          const uint32_t sl = ring_seq % KL, lph = (ring_seq / KL) & 1u;
+          ok = WAIT(bar_lse_empty(sl), lph ^ 1u, ST_WAIT_LSE_EMPTY);
+          if (!ok) break;
+          if (lane == 0) {
+            ptx::mbar_arrive_expect_tx(bar_lse_full(sl), L::kLseBytes);
+            ptx::bulk_load(s_lse + sl * L::kLseBytes,
+                           p.neg_lse + (size_t)g.bh * p.m_pad + (size_t)t * kTile, L::kLseBytes,
+                           bar_lse_full(sl));
+          }
+          __syncwarp();
+        }
       }
       g = g_next;
     }
@@ -571,14 +590,14 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
         const uint32_t ts = (uint32_t)(t - g.t_lo[a] + g.par) & 1u;
         // with tile ownership a warpgroup folds every other tile of its sub-tile
         const bool active = in_range && (!kTileOwner || (int)ts == part);
-        const uint32_t s = rs % KR, rph = (rs / KR) & 1u;
-        // columns pass: the ring slot also carries the tile's lse values, which the folding
-        // warps read.  Every softmax warp waits for every slot and releases it, whether or not
-        // it folds the tile: a warp that skipped phases of a barrier could pass a later
-        // parity wait on a stale phase and release the slot before it had been filled.
+        const uint32_t sl = rs % KL, lph = (rs / KL) & 1u;
+        // columns pass: the folding warps read the tile's lse values from the lse ring.  Every
+        // softmax warp waits for every lse slot and releases it, whether or not it folds the
+        // tile: a warp that skipped phases of a barrier could pass a later parity wait on a
+        // stale phase and release the slot before it had been filled.
         constexpr bool holds_slot = PHASE == PH_COLS;
         if (holds_slot) {
-          ok = WAIT(bar_ring_full(s), rph, ST_WAIT_RING_FULL_SM);
+          ok = WAIT(bar_lse_full(sl), lph, ST_WAIT_RING_FULL_SM);
           if (!ok) break;
         }
         if (active) {
@@ -593,7 +612,7 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
           const bool need_mask = (PHASE != PH_DUMP) && (t >= mask_from || t < mask_until);
           const int lim_lo = valid_lo - c0, lim_hi = valid_hi - c0;
           const float* lse_s =
-              reinterpret_cast<const float*>(smem + L::off_lse + s * L::kLseBytes) + col_base;
+              reinterpret_cast<const float*>(smem + L::off_lse + sl * L::kLseBytes) + col_base;
 
           constexpr int kChunk = (PHASE == PH_COLS) ? kChunkCols : kChunkRows;
           uint32_t ra[kChunk];
@@ -641,7 +660,7 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
         }
         if (holds_slot) {
           __syncwarp();
-          if (lane == 0) ptx::mbar_arrive(bar_ring_empty(s));
+          if (lane == 0) ptx::mbar_arrive(bar_lse_empty(sl));
         }
       }
       ring_base += (uint32_t)(g.c_hi - g.c_lo);
