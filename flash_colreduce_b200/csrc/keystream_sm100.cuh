@@ -120,6 +120,7 @@ keystream_kernel(const __grid_constant__ CUtensorMap tmap_q,
 
   if (warp == kKsProducerWarp) {
     // ------------------------------------------------------------ TMA warp
+    PROF_DECL();
     uint32_t ring_seq = 0, q_seq = 0;
     int cur_bh = -1;
     bool ok = true;
@@ -159,6 +160,7 @@ keystream_kernel(const __grid_constant__ CUtensorMap tmap_q,
     }
   } else if (warp == kKsMmaWarp) {
     // ------------------------------------------------------------- MMA warp
+    PROF_DECL();
     uint32_t ring_seq = 0, q_seq = 0;
     uint32_t tm_par = 0;  // bit b: parity of the next use of accumulator buffer b
     int cur_bh = -1;
@@ -226,6 +228,7 @@ keystream_kernel(const __grid_constant__ CUtensorMap tmap_q,
     // -------------------------------------------------------- softmax warps
     // Warpgroup wg folds the tiles that land in accumulator buffer wg: tile t of an item goes
     // to buffer (t - t_lo) mod 4, a property of the item.
+    PROF_DECL();
     const int wg = warp >> 2;
     const int tid_wg = (warp & 3) * 32 + lane;
     const uint32_t lane_field = (uint32_t)((warp & 3) * 32) << 16;
