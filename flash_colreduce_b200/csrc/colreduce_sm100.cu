@@ -300,31 +300,31 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(prof_g0));
 #endif
 
-  if (threadIdx.x == 0) {
-    for (int i = 0; i < KS; ++i) {
-      ptx::mbar_init(bar_stat_full(i), 1);
-      ptx::mbar_init(bar_stat_empty(i), kMmaWarps);
+  if (warp == 0) {  // the lanes of one warp initialise the barriers side by side
+    if (lane < KS) {
+      ptx::mbar_init(bar_stat_full(lane), 1);
+      ptx::mbar_init(bar_stat_empty(lane), kMmaWarps);
     }
-    for (int i = 0; i < KR; ++i) {
-      ptx::mbar_init(bar_ring_full(i), 1);
-      ptx::mbar_init(bar_ring_empty(i), kMmaWarps);
+    if (lane < KR) {
+      ptx::mbar_init(bar_ring_full(lane), 1);
+      ptx::mbar_init(bar_ring_empty(lane), kMmaWarps);
     }
-    for (int i = 0; i < KL; ++i) {
-      ptx::mbar_init(bar_lse_full(i), 1);
-      ptx::mbar_init(bar_lse_empty(i), kSoftmaxWarps);
+    if (lane < KL) {
+      ptx::mbar_init(bar_lse_full(lane), 1);
+      ptx::mbar_init(bar_lse_empty(lane), kSoftmaxWarps);
     }
-    for (int a = 0; a < 2; ++a)
-      for (int ts = 0; ts < 2; ++ts) {
-        ptx::mbar_init(bar_tm_full(a, ts), 1);
-        ptx::mbar_init(bar_tm_empty(a, ts), kTileOwner ? 4 : 4 * kColSplit);
-        ptx::mbar_init(bar_merge_full(a, ts), kColSplit > 1 ? 4 * (kColSplit - 1) : 1);
-        ptx::mbar_init(bar_merge_empty(a, ts), 4);
-      }
-    for (int i = 0; i < KI; ++i) {
-      ptx::mbar_init(bar_sched_full(i), 1);
-      ptx::mbar_init(bar_sched_empty(i), kMmaWarps + kSoftmaxWarps);
+    if (lane < 4) {
+      const uint32_t a = (uint32_t)lane >> 1, ts = (uint32_t)lane & 1u;
+      ptx::mbar_init(bar_tm_full(a, ts), 1);
+      ptx::mbar_init(bar_tm_empty(a, ts), kTileOwner ? 4 : 4 * kColSplit);
+      ptx::mbar_init(bar_merge_full(a, ts), kColSplit > 1 ? 4 * (kColSplit - 1) : 1);
+      ptx::mbar_init(bar_merge_empty(a, ts), 4);
     }
-    *abort_flag = 0;
+    if (lane < KI) {
+      ptx::mbar_init(bar_sched_full(lane), 1);
+      ptx::mbar_init(bar_sched_empty(lane), kMmaWarps + kSoftmaxWarps);
+    }
+    if (lane == 0) *abort_flag = 0;
     ptx::fence_mbar_init();
   }
   if (warp == kMmaWarp) {
@@ -372,13 +372,15 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
       __syncwarp();
       return true;
     };
-    auto fetch_index = [&]() {  // next work-item index from the global counter (all lanes get it)
-      int v = 0;
-      if (lane == 0) v = (int)gridDim.x + atomicAdd(p.sched_counter, 1);
-      return __shfl_sync(0xffffffffu, v, 0);
+    // Lane 0 asks the global counter for an index one item early and leaves the answer in
+    // `pending`; it is broadcast only when the next iteration needs it, so the warp never
+    // stalls on the atomic's round trip.
+    int pending = 0;
+    auto issue_fetch = [&]() {
+      if (lane == 0) pending = (int)gridDim.x + atomicAdd(p.sched_counter, 1);
     };
-    int item = (int)blockIdx.x;
-    int item_next = fetch_index();
+    const int item = (int)blockIdx.x;
+    issue_fetch();
     Item g;
     g.bh = -1;
     if (item < p.n_items) g = decode_item<PHASE == PH_COLS>(p, item);
@@ -407,12 +409,15 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
       }
       __syncwarp();
       if (last) break;
-      // the item after this one, and the index of the one after that
+      // the item after this one (its index was requested an iteration ago), and a request
+      // for the index of the one after that
+      const int item_next = __shfl_sync(0xffffffffu, pending, 0);
       Item g_next;
       g_next.bh = -1;
-      if (item_next < p.n_items) g_next = decode_item<PHASE == PH_COLS>(p, item_next);
-      item = item_next;
-      item_next = (item < p.n_items) ? fetch_index() : item;
+      if (item_next < p.n_items) {
+        g_next = decode_item<PHASE == PH_COLS>(p, item_next);
+        issue_fetch();
+      }
       if (kAhead) {
         if (g_next.bh >= 0) ok = load_stationary(g_next, item_seq + 1);
       } else {
