@@ -73,6 +73,7 @@ class Plan(C.Structure):
         ("off_part_m", C.c_int64), ("off_part_l", C.c_int64), ("off_part_out", C.c_int64),
         ("workspace_bytes", C.c_int64),
         ("key_stream", C.c_int32), ("key_chunks", C.c_int32),
+        ("off_scores", C.c_int64), ("score_cache", C.c_int32), ("reserved", C.c_int32),
     ]
 
 

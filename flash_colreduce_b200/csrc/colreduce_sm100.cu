@@ -116,7 +116,7 @@ struct PassParams : PassGeom {
   float* part_m;   // [n_split][BH][m_pad]
   float* part_l;   // [n_split][BH][m_pad]
   float* part_out; // [n_split][BH][n_pad]
-  float* dump;     // [BH][m_pad][n_pad]   (PH_DUMP)
+  float* dump;     // [BH][m_pad][n_pad] (PH_DUMP); [BH][M][n_pad] score cache of the key-streaming rows pass
   void* out;       // [BH][N] of out_dtype
   int out_dtype;
   int mean_mode;   // 0: none, 1: divide by div_M, 2: causal rule
@@ -818,6 +818,49 @@ __global__ void final_reduce_kernel(const float* __restrict__ part, PassParams p
   }
 }
 
+// Columns pass from cached scores (decode with M <= 16): thread = key column, the M raw scores of
+// the column are read from the array the rows pass wrote, P = 2^(s*scale2 - lse_i) is folded in
+// query order (flash_colreduce/flash.py:120-124), then the mean divisor and the cast (:377-385).
+template <int RED>
+__global__ void __launch_bounds__(256)
+scores_reduce_kernel(const float* __restrict__ scores, PassParams p, int blocks_per_head) {
+  __shared__ float nl[16];
+  ptx::grid_dependency_wait();
+  const int bh = (int)(blockIdx.x / (unsigned)blocks_per_head);
+  // four consecutive keys per thread: one 16-byte load per query row
+  const int j0 = ((int)(blockIdx.x % (unsigned)blocks_per_head) * 256 + (int)threadIdx.x) * 4;
+  if ((int)threadIdx.x < p.M) nl[threadIdx.x] = p.neg_lse[(size_t)bh * p.m_pad + threadIdx.x];
+  __syncthreads();
+  if (j0 >= p.N) return;
+  const float* col = scores + (size_t)bh * p.M * p.n_pad + j0;  // n_pad is a multiple of 128: aligned
+  float acc[4];
+  int lo[4];  // queries lo <= i < M attend key j
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    acc[e] = (RED == RED_MAX) ? -INFINITY : 0.f;
+    lo[e] = p.causal ? max(j0 + e - p.off, 0) : 0;
+  }
+  for (int i = lo[0]; i < p.M; ++i) {  // lo[0] is the smallest of the four
+    const float4 s4 = *reinterpret_cast<const float4*>(col + (size_t)i * p.n_pad);
+    const float sv[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float x = fmaf(sv[e], p.scale2, nl[i]);
+      if (RED == RED_MAX)
+        acc[e] = (i >= lo[e]) ? fmaxf(acc[e], x) : acc[e];
+      else
+        acc[e] += (i >= lo[e]) ? ptx::ex2(x) : 0.f;
+    }
+  }
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    if (j0 + e >= p.N) break;
+    float v = (RED == RED_MAX) ? ptx::ex2(acc[e]) : acc[e];
+    if (p.mean_mode) v = v / mean_divisor(p, j0 + e);
+    store_out(p.out, p.out_dtype, (size_t)bh * p.N + j0 + e, v);
+  }
+}
+
 // Mean divisor + cast of an already reduced fp32 (B*H, N) array.
 __global__ void finalize_kernel(const float* __restrict__ acc, PassParams p) {
   const size_t total = (size_t)p.BH * p.N;
@@ -1036,14 +1079,20 @@ static int launch_keystream_d(int d_pad, const CUtensorMap& map_q, const CUtenso
   return launch_keystream<PHASE, 128, RED>(map_q, map_k, pp, ctas, stream);
 }
 
+// Bytes a plan cannot do without: the score cache is the last region of the workspace and is
+// optional (without it the columns pass sweeps K a second time).
+static int64_t min_workspace_bytes(const fcr_plan& pl) {
+  return pl.score_cache ? pl.off_scores : pl.workspace_bytes;
+}
+
 static int check_workspace(const fcr_plan& pl, const void* ws, size_t ws_bytes) {
   if (!ws) return fail(FCR_ERR_WORKSPACE, "workspace is null");
   if ((reinterpret_cast<uintptr_t>(ws) & 255u) != 0)
     return fail(FCR_ERR_WORKSPACE, "workspace must be 256-byte aligned");
-  if ((int64_t)ws_bytes < pl.workspace_bytes)
+  if ((int64_t)ws_bytes < min_workspace_bytes(pl))
     return fail(FCR_ERR_WORKSPACE, "workspace of " + std::to_string(ws_bytes) +
                                        " bytes is smaller than the required " +
-                                       std::to_string(pl.workspace_bytes));
+                                       std::to_string(min_workspace_bytes(pl)));
   return FCR_OK;
 }
 
@@ -1217,6 +1266,9 @@ int fcr_colreduce(const fcr_problem* problem, const void* q, const void* k, void
       pp.fold_cols = (int)align_up64(pr.M, kChunkCols);
     };
     fill(false);
+    // the score cache is used when the caller's workspace has room for it
+    const bool use_cache = pl.score_cache && (int64_t)workspace_bytes >= pl.workspace_bytes;
+    if (use_cache) pp.dump = reinterpret_cast<float*>(ws + pl.off_scores);
     rc = launch_keystream_d<PH_ROWS, RED_SUM>(pl.d_pad, map_q, map_k, pp, pl.row_ctas, stream);
     if (rc != FCR_OK) return rc;
     {
@@ -1233,6 +1285,22 @@ int fcr_colreduce(const fcr_problem* problem, const void* q, const void* k, void
     pp.out_dtype = out_dtype;
     fill_mean(pp, pr.reduction, pr.is_causal, pr.mean_M > 0 ? pr.mean_M : pr.M,
               pr.mean_N > 0 ? pr.mean_N : pr.N);
+    if (use_cache) {
+      const float* scores = reinterpret_cast<const float*>(ws + pl.off_scores);
+      const int bph = (pr.N + 1023) / 1024;  // 256 threads x 4 keys
+      const long long blocks = (long long)pp.BH * bph;
+      if (blocks > 0x7fffffffLL) return fail(FCR_ERR_UNSUPPORTED, "problem has too many key blocks");
+      if (pr.reduction == FCR_MAX)
+        e = launch_kernel(scores_reduce_kernel<RED_MAX>, dim3((unsigned)blocks), dim3(256), 0, stream, true,
+                          scores, pp, bph);
+      else
+        e = launch_kernel(scores_reduce_kernel<RED_SUM>, dim3((unsigned)blocks), dim3(256), 0, stream, true,
+                          scores, pp, bph);
+      if (e == cudaSuccess) e = cudaGetLastError();
+      if (e != cudaSuccess) return cuda_fail(e, "scores_reduce launch");
+      trace_mark(2, stream);
+      return FCR_OK;
+    }
     if (pr.reduction == FCR_MAX)
       rc = launch_keystream_d<PH_COLS, RED_MAX>(pl.d_pad, map_q, map_k, pp, pl.col_ctas, stream);
     else
@@ -1420,9 +1488,9 @@ int fcr_colreduce_static(const fcr_problem* problem, const void* q, const void* 
   fcr_plan pl;
   int rc = fcr_plan_problem(problem, 0, &pl);
   if (rc != FCR_OK) return rc;
-  if ((size_t)pl.workspace_bytes > kStaticScratchBytes)
+  if ((size_t)min_workspace_bytes(pl) > kStaticScratchBytes)
     return fail(FCR_ERR_WORKSPACE,
-                "this problem needs " + std::to_string(pl.workspace_bytes) +
+                "this problem needs " + std::to_string(min_workspace_bytes(pl)) +
                     " bytes of scratch but the built-in scratch holds " +
                     std::to_string(kStaticScratchBytes) +
                     " (FCR_STATIC_SCRATCH_BYTES); use fcr_colreduce with a caller-owned workspace");

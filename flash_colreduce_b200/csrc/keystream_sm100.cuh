@@ -277,6 +277,15 @@ keystream_kernel(const __grid_constant__ CUtensorMap tmap_q,
               __syncwarp();
               if (lane == 0) ptx::mbar_arrive(bar_tm_empty(wg));
             }
+            if (p.dump != nullptr && mine < p.M) {
+              // score cache: this query's raw scores against the 64 keys of the chunk
+              float4* dst = reinterpret_cast<float4*>(p.dump + ((size_t)bh * p.M + mine) * p.n_pad +
+                                                      (size_t)t * kTile + c * kChunkRows);
+#pragma unroll
+              for (int q4 = 0; q4 < kChunkRows / 4; ++q4)
+                dst[q4] = make_float4(__uint_as_float(ra[4 * q4]), __uint_as_float(ra[4 * q4 + 1]),
+                                      __uint_as_float(ra[4 * q4 + 2]), __uint_as_float(ra[4 * q4 + 3]));
+            }
             if (need_mask)
               rows_chunk<true, kChunkRows>(ra, p.scale2, lim_hi - kChunkRows * c, m_run, l_run);
             else

@@ -311,6 +311,14 @@ inline int plan_problem(const fcr_problem& p, int num_sms, fcr_plan& pl, std::st
     pl.off_part_out = o;
     o += align_up64((int64_t)pl.col_splits * BH * pl.n_pad * 4, 256);
   }
+  // Decode with a handful of queries: 4*M bytes of scores per key are far fewer than the key's
+  // own bytes, so the rows pass keeps them and the second sweep over K is not needed.
+  const int64_t score_bytes = BH * p.M * (int64_t)pl.n_pad * 4;
+  if (pl.key_stream && p.M <= 16 && score_bytes <= (1LL << 31)) {
+    pl.score_cache = 1;
+    pl.off_scores = o;
+    o += align_up64(score_bytes, 256);
+  }
   pl.workspace_bytes = o;
   return FCR_OK;
 }

@@ -103,6 +103,14 @@ typedef struct fcr_plan {
    * row_splits = 4 * key_chunks partial (max, sum) states per row, the columns pass none. */
   int32_t key_stream;       /* 1 when the key-streaming kernels run this problem */
   int32_t key_chunks;       /* work items per head and pass */
+  /* Score cache (key streaming with M <= 16): the rows pass also writes the raw fp32 scores, 4*M bytes
+   * per key against the 2*D bytes of the key itself, and the columns are reduced from that array by
+   * a plain kernel instead of a second sweep over K: the keys are read from HBM once. */
+  int64_t off_scores;       /* float[B*H][M][n_pad] raw scores Q.K^T (score_cache only); the last region of the
+                             * workspace and optional: a workspace of only off_scores bytes is accepted, the
+                             * columns pass then sweeps K a second time */
+  int32_t score_cache;      /* 1 when the columns are reduced from cached scores */
+  int32_t reserved;
 } fcr_plan;
 
 /* Library version string, e.g. "0.1.0". */

@@ -229,6 +229,38 @@ def test_decode_full_size_properties():
         assert (mean <= mx * (1 + 2e-3) + 1e-6).all()
 
 
+def test_score_cache_is_optional():
+    """M <= 16 decode: with the full workspace the columns are reduced from the cached scores, with a
+    workspace that ends before the cache (plan.off_scores bytes) by a second sweep over K."""
+    import ctypes as C
+
+    from flash_colreduce_b200 import _native as nat
+
+    dev = _dev()
+    b, h, m, n, d = 2, 3, 5, 3000, 64
+    q, k = _rand((b, h, m, d), 56), _rand((b, h, n, d), 57)
+    qd, kd = q.to(dev), k.to(dev)
+    stream = torch.cuda.current_stream().cuda_stream
+    for red in ("sum", "max"):
+        for causal in (False, True):
+            pr = nat.make_problem(b, h, m, n, d, qd.stride(), kd.stride(), nat.FCR_F16, nat.REDUCTION_CODES[red],
+                                  causal, 1 / math.sqrt(d))
+            pl = nat.plan(pr, 0)
+            assert pl.key_stream == 1 and pl.score_cache == 1 and 0 < pl.off_scores < pl.workspace_bytes
+            want = oracle_colreduce(q, k, red, causal)
+            for ws_bytes in (pl.workspace_bytes, pl.off_scores):
+                ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+                out = torch.empty(b, h, n, dtype=torch.float32, device=dev)
+                nat.check(nat.lib.fcr_colreduce(C.byref(pr), qd.data_ptr(), kd.data_ptr(), out.data_ptr(), nat.FCR_F32,
+                                                ws.data_ptr(), ws.numel(), stream), "fcr_colreduce")
+                nat.check(nat.lib.fcr_read_device_status(ws.data_ptr(), stream, None), "device status")
+                assert_parity(out, want, red)
+            too_small = torch.empty(pl.off_scores - 256, dtype=torch.uint8, device=dev)
+            rc = nat.lib.fcr_colreduce(C.byref(pr), qd.data_ptr(), kd.data_ptr(), out.data_ptr(), nat.FCR_F32,
+                                       too_small.data_ptr(), too_small.numel(), stream)
+            assert rc == nat.FCR_ERR_WORKSPACE
+
+
 def test_decode_shapes_other_dtypes():
     from flash_colreduce_b200 import flash_colreduce
 
