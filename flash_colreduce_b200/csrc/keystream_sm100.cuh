@@ -7,7 +7,10 @@
 //   rows pass     S = Q K^T, lanes = queries: thread owns a query row and folds
 //                 every fourth key tile of the work item into (max, sum); the four
 //                 warpgroups leave four partial states, combined by
-//                 combine_lse_kernel (flash_colreduce/flash.py:71-78).
+//                 combine_lse_kernel (flash_colreduce/flash.py:71-78).  With at most
+//                 16 queries it also stores the raw scores (PassParams::dump), from
+//                 which scores_reduce_kernel reduces the columns without a second
+//                 sweep over the keys.
 //   columns pass  S^T = K Q^T, lanes = keys: thread owns a key column; one tile
 //                 holds every query, so the column's reduction is complete after
 //                 one tile and is written straight to the output
