@@ -277,6 +277,36 @@ def test_decode_shapes_other_dtypes():
             assert_parity(got, oracle_colreduce(q, k, red, causal), red)
 
 
+@pytest.mark.parametrize("world,heads,m,n", [(4, 2, 1000, 1300), (8, 1, 2048, 2048), (2, 5, 300, 700), (4, 1, 100, 4096)])
+def test_shards_of_several_ranks_on_one_gpu(world, heads, m, n):
+    """The shard plans of a multi-GPU run (row slices with explicit mask offsets, or head ranges), executed
+    rank after rank on this GPU and combined as the all-reduce would."""
+    import dataclasses
+
+    from flash_colreduce_b200 import finalize_scores
+    from flash_colreduce_b200.sharding import plan_shards, sharded_colreduce
+
+    dev = _dev()
+    q, k = _rand((1, heads, m, 64), 70), _rand((1, heads, n, 64), 71)
+    for red in ("sum", "mean", "max"):
+        for causal in (False, True):
+            acc = None
+            for rank in range(world):
+                spec = plan_shards(heads, m, world, rank)
+                if spec.heads == 0:
+                    continue
+                alone = dataclasses.replace(spec, world=1)  # no collective: the partial comes back as it is
+                part = sharded_colreduce(q[:, spec.head_lo:spec.head_hi].to(dev), k[:, spec.head_lo:spec.head_hi].to(dev),
+                                         red, causal, spec=alone, total_heads=heads,
+                                         finalize_fn=lambda a, *rest: a)
+                if acc is None:
+                    acc = part
+                else:
+                    acc = torch.maximum(acc, part) if red == "max" else acc + part
+            got = finalize_scores(acc[None].contiguous(), m, red, causal, torch.float32)
+            assert_parity(got, oracle_colreduce(q, k, red, causal), red)
+
+
 def test_zero_scale_gives_uniform_rows():
     dev = _dev()
     q, k = _rand((1, 2, 100, 64), 32), _rand((1, 2, 300, 64), 33)
