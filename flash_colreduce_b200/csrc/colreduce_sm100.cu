@@ -136,9 +136,14 @@ struct SmemLayout {
   static constexpr int kTileBytes = kTile * DPAD * 2;
   static constexpr int kHalves = DPAD / 64;     // 64-element (128-byte) column slabs per tile
   static constexpr int kHalfBytes = kTile * 128;
-  // 512-byte rows (DPAD 256) leave room for one stage of each only: correct, not fast.
+  // 512-byte rows (DPAD 256): the stationary block takes 128 KB, which leaves 64 KB for streaming.
+  // A streamed tile then travels as two pieces of 256 bytes per row (two slabs), one ring slot
+  // each, and the MMAs of a piece run while the next piece is loaded.
+  static constexpr int kPieces = DPAD == 256 ? 2 : 1;        // ring slots per streamed tile
+  static constexpr int kSlotBytes = kTileBytes / kPieces;    // bytes of a ring slot
+  static constexpr int kSlotHalves = kHalves / kPieces;      // 128-byte slabs per ring slot
   static constexpr int KS = DPAD == 256 ? 1 : ((DPAD == 64 || SHORT) ? 2 : 1);  // stationary stages
-  static constexpr int KR = DPAD == 256 ? 1 : (DPAD == 64 ? 6 : (SHORT ? 2 : 4));  // streamed ring stages
+  static constexpr int KR = DPAD == 256 ? 2 : (DPAD == 64 ? 6 : (SHORT ? 2 : 4));  // streamed ring slots
   static constexpr int kLseBytes = kTile * 4;
   // The lse values of a streamed query tile (columns pass) travel in a ring of their own, deeper
   // than the tile ring: the tile slots are then released by the MMAs alone and the loads run
@@ -146,7 +151,7 @@ struct SmemLayout {
   static constexpr int KL = KR + 4;  // tiles in the ring + tiles being folded + slack
   static constexpr int off_stat = 0;
   static constexpr int off_ring = off_stat + KS * kSubTiles * kTileBytes;
-  static constexpr int off_lse = off_ring + KR * kTileBytes;
+  static constexpr int off_lse = off_ring + KR * kSlotBytes;
   static constexpr int off_merge = off_lse + KL * kLseBytes;  // float2 [2 slots][kSubTiles][kTile]
   static constexpr int kMergeBytes = (kColSplit > 1) ? 2 * kSubTiles * kTile * 8 : 0;
   static constexpr int off_bars = off_merge + kMergeBytes;
@@ -354,7 +359,7 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
     // kernel.  With two stationary stages the stationary tiles of item i+1 are
     // requested before the streamed tiles of item i, i.e. a whole item ahead.
     constexpr bool kAhead = KS >= 2;
-    uint32_t ring_seq = 0, item_seq = 0;
+    uint32_t ring_seq = 0, tile_seq = 0, item_seq = 0;  // ring slots, streamed tiles, items so far
     bool ok = true;
     auto load_stationary = [&](const Item& g, uint32_t seq) {
       const int b = g.bh / p.H, h = g.bh - b * p.H;
@@ -425,20 +430,25 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
       }
       if (!ok) break;
       const int b = g.bh / p.H, h = g.bh - b * p.H;
-      for (int t = g.c_lo; t < g.c_hi; ++t, ++ring_seq) {
-        const uint32_t s = ring_seq % KR, ph = (ring_seq / KR) & 1u;
-        ok = WAIT(bar_ring_empty(s), ph ^ 1u, ST_WAIT_RING_EMPTY);
-        if (!ok) break;
-        if (lane == 0) {
-          ptx::mbar_arrive_expect_tx(bar_ring_full(s), L::kTileBytes);
+      for (int t = g.c_lo; t < g.c_hi; ++t, ++tile_seq) {
 #pragma unroll
-          for (int hf = 0; hf < L::kHalves; ++hf)
-            ptx::tma_load_4d(s_ring + s * L::kTileBytes + hf * L::kHalfBytes, &tmap_strm,
-                             bar_ring_full(s), hf * p.slab_elems, t * kTile, h, b);
+        for (int piece = 0; piece < L::kPieces; ++piece, ++ring_seq) {
+          const uint32_t s = ring_seq % KR, ph = (ring_seq / KR) & 1u;
+          ok = WAIT(bar_ring_empty(s), ph ^ 1u, ST_WAIT_RING_EMPTY);
+          if (!ok) break;
+          if (lane == 0) {
+            ptx::mbar_arrive_expect_tx(bar_ring_full(s), L::kSlotBytes);
+#pragma unroll
+            for (int hf = 0; hf < L::kSlotHalves; ++hf)
+              ptx::tma_load_4d(s_ring + s * L::kSlotBytes + hf * L::kHalfBytes, &tmap_strm,
+                               bar_ring_full(s), (piece * L::kSlotHalves + hf) * p.slab_elems,
+                               t * kTile, h, b);
+          }
+          __syncwarp();
         }
-        __syncwarp();
+        if (!ok) break;
         if (PHASE == PH_COLS) {  // the tile's lse values, into their own ring
-          const uint32_t sl = ring_seq % KL, lph = (ring_seq / KL) & 1u;
+          const uint32_t sl = tile_seq % KL, lph = (tile_seq / KL) & 1u;
           ok = WAIT(bar_lse_empty(sl), lph ^ 1u, ST_WAIT_LSE_EMPTY);
           if (!ok) break;
           if (lane == 0) {
@@ -484,48 +494,61 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
       if (!ok) break;
       ptx::tc_fence_after_sync();
       const uint32_t a_addr = s_stat + (ks * kSubTiles + a) * L::kTileBytes;
-      for (int t = g.c_lo; ok && t < g.c_hi; ++t, ++ring_seq) {
-        const uint32_t s = ring_seq % KR, ph = (ring_seq / KR) & 1u;
-        ok = WAIT(bar_ring_full(s), ph, ST_WAIT_RING_FULL);
-        if (!ok) break;
+      for (int t = g.c_lo; ok && t < g.c_hi; ++t) {
         const uint32_t ts = (uint32_t)(t - g.t_lo[a] + g.par) & 1u;
-        if (t >= g.t_lo[a] && t < g.t_hi[a] && (!kMmaPerBuffer || (int)ts == my_buf)) {
-          const uint32_t tph = (ts ? tm_use[1] : tm_use[0]) & 1u;
-          ok = WAIT(bar_tm_empty(a, ts), tph ^ 1u, ST_WAIT_TMEM_EMPTY);
-          if (!ok) break;
-          ptx::tc_fence_after_sync();
-          PROF_T0();
-          if (lane == 0) {
-            const uint32_t d = tmem_base + (uint32_t)(a * 2 + ts) * kTile;
-            const uint32_t b_addr = s_ring + s * L::kTileBytes;
-            // One instruction per 32 bytes of each operand row: 16 halves or 8 TF32 values.
-            // The operand kind is chosen once, outside the unrolled sequence.
-            auto issue_steps = [&](auto as_tf32) {
+        const bool my_tile =
+            t >= g.t_lo[a] && t < g.t_hi[a] && (!kMmaPerBuffer || (int)ts == my_buf);
+        // a streamed tile arrives in kPieces ring slots (one, or two halves of the row width)
 #pragma unroll
-              for (int kk = 0; kk < DPAD / 16; ++kk) {
-                const uint32_t koff = (uint32_t)(kk >> 2) * L::kHalfBytes + (uint32_t)(kk & 3) * 32u;
-                if constexpr (decltype(as_tf32)::value)
-                  ptx::umma_tf32(d, ptx::smem_desc_sw128(a_addr + koff),
-                                 ptx::smem_desc_sw128(b_addr + koff), p.idesc, kk > 0 ? 1u : 0u);
-                else
-                  ptx::umma_f16(d, ptx::smem_desc_sw128(a_addr + koff),
-                                ptx::smem_desc_sw128(b_addr + koff), p.idesc, kk > 0 ? 1u : 0u);
-              }
-            };
-            if (p.tf32)
-              issue_steps(std::true_type{});
-            else
-              issue_steps(std::false_type{});
-            ptx::umma_commit(bar_tm_full(a, ts));
-            ptx::umma_commit(bar_ring_empty(s));
+        for (int piece = 0; piece < L::kPieces; ++piece, ++ring_seq) {
+          const uint32_t s = ring_seq % KR, ph = (ring_seq / KR) & 1u;
+          ok = WAIT(bar_ring_full(s), ph, ST_WAIT_RING_FULL);
+          if (!ok) break;
+          if (my_tile) {
+            if (piece == 0) {
+              const uint32_t tph = (ts ? tm_use[1] : tm_use[0]) & 1u;
+              ok = WAIT(bar_tm_empty(a, ts), tph ^ 1u, ST_WAIT_TMEM_EMPTY);
+              if (!ok) break;
+            }
+            ptx::tc_fence_after_sync();
+            PROF_T0();
+            if (lane == 0) {
+              const uint32_t d = tmem_base + (uint32_t)(a * 2 + ts) * kTile;
+              const uint32_t b_addr = s_ring + s * L::kSlotBytes;
+              // One instruction per 32 bytes of each operand row: 16 halves or 8 TF32 values.
+              // The operand kind is chosen once, outside the unrolled sequence.
+              constexpr int kSteps = DPAD / 16 / L::kPieces;  // instructions per ring slot
+              auto issue_steps = [&](auto as_tf32) {
+#pragma unroll
+                for (int kq = 0; kq < kSteps; ++kq) {
+                  const int kk = piece * kSteps + kq;  // step within the whole row
+                  const uint32_t a_off = (uint32_t)(kk >> 2) * L::kHalfBytes + (uint32_t)(kk & 3) * 32u;
+                  const uint32_t b_off = (uint32_t)(kq >> 2) * L::kHalfBytes + (uint32_t)(kq & 3) * 32u;
+                  if constexpr (decltype(as_tf32)::value)
+                    ptx::umma_tf32(d, ptx::smem_desc_sw128(a_addr + a_off),
+                                   ptx::smem_desc_sw128(b_addr + b_off), p.idesc, kk > 0 ? 1u : 0u);
+                  else
+                    ptx::umma_f16(d, ptx::smem_desc_sw128(a_addr + a_off),
+                                  ptx::smem_desc_sw128(b_addr + b_off), p.idesc, kk > 0 ? 1u : 0u);
+                }
+              };
+              if (p.tf32)
+                issue_steps(std::true_type{});
+              else
+                issue_steps(std::false_type{});
+              if (piece + 1 == L::kPieces) ptx::umma_commit(bar_tm_full(a, ts));
+              ptx::umma_commit(bar_ring_empty(s));
+            }
+            __syncwarp();
+            PROF_ADD(25);
+            if (piece + 1 == L::kPieces) {
+              if (ts) ++tm_use[1]; else ++tm_use[0];
+            }
+          } else {
+            // not this sub-tile's tile: the slot is released as soon as it has been filled
+            if (lane == 0) ptx::mbar_arrive(bar_ring_empty(s));
+            __syncwarp();
           }
-          __syncwarp();
-          PROF_ADD(25);
-          if (ts) ++tm_use[1]; else ++tm_use[0];
-        } else {
-          // not this sub-tile's tile: the slot is released as soon as it has been filled
-          if (lane == 0) ptx::mbar_arrive(bar_ring_empty(s));
-          __syncwarp();
         }
       }
       if (!ok) break;
