@@ -1099,6 +1099,7 @@ template <int PHASE, int RED>
 static int launch_keystream_d(int d_pad, const CUtensorMap& map_q, const CUtensorMap& map_k,
                               const PassParams& pp, int ctas, cudaStream_t stream) {
   if (d_pad == 64) return launch_keystream<PHASE, 64, RED>(map_q, map_k, pp, ctas, stream);
+  if (d_pad == 256) return launch_keystream<PHASE, 256, RED>(map_q, map_k, pp, ctas, stream);
   return launch_keystream<PHASE, 128, RED>(map_q, map_k, pp, ctas, stream);
 }
 

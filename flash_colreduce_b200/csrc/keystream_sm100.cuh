@@ -44,7 +44,7 @@ struct KeyStreamSmem {
   static constexpr int kTileBytes = kTile * DPAD * 2;
   static constexpr int kHalves = DPAD / 64;
   static constexpr int kHalfBytes = kTile * 128;
-  static constexpr int KR = DPAD == 64 ? 8 : 5;  // key tiles in flight
+  static constexpr int KR = DPAD == 64 ? 8 : (DPAD == 128 ? 5 : 2);  // key tiles in flight
   static constexpr int kLseBytes = kTile * 4;
   static constexpr int off_q = 0;
   static constexpr int off_ring = off_q + kTileBytes;

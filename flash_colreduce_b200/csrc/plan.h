@@ -261,7 +261,7 @@ inline int plan_problem(const fcr_problem& p, int num_sms, fcr_plan& pl, std::st
   pl.key_stream = 0;
   pl.key_chunks = 0;
   const int64_t key_tiles = pl.n_pad / kTile;
-  if (pl.m_pad == kTile && key_tiles >= 8 && pl.d_pad <= 128) {
+  if (pl.m_pad == kTile && key_tiles >= 8) {
     int best_s = 1;
     int64_t best_cost = -1;
     for (int64_t s = 1; s <= std::min<int64_t>(key_tiles, 256); ++s) {

@@ -192,7 +192,7 @@ def test_many_items_per_cta_with_a_skipped_half_block(d):
 
 @pytest.mark.parametrize("b,h,m,n,d", [(1, 2, 1, 1024, 128), (2, 3, 7, 1500, 64), (1, 4, 64, 4099, 128),
                                        (1, 2, 100, 2048, 72), (1, 1, 128, 8192, 128), (3, 50, 33, 1027, 64),
-                                       (1, 160, 128, 1024, 128)])
+                                       (1, 160, 128, 1024, 128), (2, 3, 50, 2048, 256), (1, 2, 9, 1100, 200)])
 def test_decode_shapes_stream_the_keys(b, h, m, n, d):
     """M <= 128 with at least 8 key tiles: the key-streaming kernels (one query tile per head kept in
     shared memory, several work items and heads per CTA in the last two cases)."""
