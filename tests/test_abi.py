@@ -70,6 +70,32 @@ def test_small_problems_are_split_to_fill_the_gpu():
     assert pl.row_splits == 1 and pl.col_splits == 1 and pl.off_part_out == 0
 
 
+def test_decode_plans_stream_the_keys():
+    # one query tile, 256 key tiles: key streaming; the last fields of the struct line up with the C layout
+    pl = nat.plan(_problem(8, 32, 64, 32768, 128, causal=True), 148)
+    assert pl.key_stream == 1 and pl.key_chunks >= 1 and pl.score_cache == 0 and pl.off_scores == 0 and pl.reserved == 0
+    assert pl.row_splits == 4 * pl.key_chunks and pl.col_splits == 1
+    assert pl.row_items == pl.col_items == 8 * 32 * pl.key_chunks
+    # at most 16 queries: the raw scores are cached at the end of the workspace
+    pl = nat.plan(_problem(8, 32, 4, 32768, 128, causal=True), 148)
+    assert pl.key_stream == 1 and pl.score_cache == 1
+    assert pl.workspace_bytes - pl.off_scores == 8 * 32 * 4 * pl.n_pad * 4
+    # too few key tiles, or more than one query tile: the general kernels
+    assert nat.plan(_problem(8, 32, 64, 512, 128, causal=True), 148).key_stream == 0
+    assert nat.plan(_problem(8, 32, 129, 32768, 128, causal=True), 148).key_stream == 0
+    # every key tile belongs to exactly one work item of its head
+    pr = _problem(1, 3, 16, 5000, 64, causal=False)
+    pl = nat.plan(pr, 148)
+    for which in (1, 2):
+        seen = {}
+        for item in range(pl.row_items):
+            it = nat.plan_item(pr, pl, which, item)
+            for t in range(*it["chunk"]):
+                assert (it["head"], t) not in seen
+                seen[(it["head"], t)] = item
+        assert len(seen) == 3 * (pl.n_pad // 128)
+
+
 def test_causal_offset_defaults_to_right_alignment():
     assert nat.plan(_problem(1, 1, 128, 1024, 64, causal=True), 148).causal_offset == 896
     assert nat.plan(_problem(1, 1, 1024, 128, 64, causal=True), 148).causal_offset == 0
