@@ -23,6 +23,7 @@
 namespace fcr {
 
 constexpr int kTopkThreads = 1024;
+static_assert(kTopkThreads == 1024, "the block-wide scan combines exactly 32 warp totals in one warp");
 constexpr int kTopkItems = 8;  // consecutive elements per thread and sweep step (one 16-byte load for 16-bit scores)
 
 // Order-preserving unsigned key of a score: 32 bits for fp32, 16 bits for fp16 / bf16 (both are
