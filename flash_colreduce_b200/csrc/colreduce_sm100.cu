@@ -1157,10 +1157,22 @@ static int topk_cluster_size(int rows, int n, int sms) {
 
 template <typename T, typename IndexT>
 static int launch_topk_t(const void* scores, int rows, int n, int k, void* indices, void* values,
-                         int cluster, cudaStream_t stream) {
+                         int cluster, int small_rows_from, cudaStream_t stream) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)rows * cluster);
   cfg.blockDim = dim3(kTopkThreads);
+  // many short rows: 256-thread blocks, several rows per SM at a time
+  const bool small = cluster == 1 && n <= 16 * kTopkThreadsSmall * kTopkItems && rows >= small_rows_from;
+  if (small) {
+    cfg.blockDim = dim3(kTopkThreadsSmall);
+    cfg.numAttrs = 0;
+    cudaError_t es = cudaLaunchKernelEx(&cfg, topk_kernel<T, IndexT, kTopkThreadsSmall, 8>,
+                                        static_cast<const T*>(scores), n, k, static_cast<IndexT*>(indices),
+                                        static_cast<T*>(values));
+    if (es == cudaSuccess) es = cudaGetLastError();
+    if (es != cudaSuccess) return cuda_fail(es, "topk launch");
+    return FCR_OK;
+  }
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -1169,7 +1181,7 @@ static int launch_topk_t(const void* scores, int rows, int n, int k, void* indic
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = cluster > 1 ? 1 : 0;  // a single CTA per row is an ordinary launch
-  cudaError_t e = cudaLaunchKernelEx(&cfg, topk_kernel<T, IndexT>, static_cast<const T*>(scores), n, k,
+  cudaError_t e = cudaLaunchKernelEx(&cfg, topk_kernel<T, IndexT, kTopkThreads, 32>, static_cast<const T*>(scores), n, k,
                                      static_cast<IndexT*>(indices), static_cast<T*>(values));
   if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "topk launch");
@@ -1184,8 +1196,8 @@ static int launch_topk(const void* scores, int rows, int n, int k, void* indices
   if (rc != FCR_OK) return rc;
   const int cluster = topk_cluster_size(rows, n, sms);
   if (index_bits == 64)
-    return launch_topk_t<T, long long>(scores, rows, n, k, indices, values, cluster, stream);
-  return launch_topk_t<T, int>(scores, rows, n, k, indices, values, cluster, stream);
+    return launch_topk_t<T, long long>(scores, rows, n, k, indices, values, cluster, 2 * sms, stream);
+  return launch_topk_t<T, int>(scores, rows, n, k, indices, values, cluster, 2 * sms, stream);
 }
 
 }  // namespace fcr

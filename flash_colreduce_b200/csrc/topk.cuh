@@ -4,7 +4,8 @@
 // kernel has no counterpart there).
 //
 // One thread-block cluster per row: a single CTA when there are enough rows to
-// fill the GPU, otherwise 2, 4 or 8 CTAs that each own a contiguous slice of the
+// fill the GPU (256 threads when the rows are short and many, so that several
+// rows share an SM), otherwise 2, 4 or 8 CTAs that each own a contiguous slice of the
 // row and exchange their 256-bin histograms and their selected-element counts
 // through distributed shared memory (cluster.sync() is a hardware barrier, there
 // is no spin wait).  The k-th largest value is found by a most-significant-byte
@@ -22,8 +23,8 @@
 
 namespace fcr {
 
-constexpr int kTopkThreads = 1024;
-static_assert(kTopkThreads == 1024, "the block-wide scan combines exactly 32 warp totals in one warp");
+constexpr int kTopkThreads = 1024;      // long rows: one CTA (or a cluster of CTAs) of 1024 threads per row
+constexpr int kTopkThreadsSmall = 256;  // many short rows: 256 threads per row, up to eight rows per SM at a time
 constexpr int kTopkItems = 8;  // consecutive elements per thread and sweep step (one 16-byte load for 16-bit scores)
 
 // Order-preserving unsigned key of a score: 32 bits for fp32, 16 bits for fp16 / bf16 (both are
@@ -73,16 +74,21 @@ __device__ __forceinline__ void topk_load8(const T* row, int i0, int n, uint32_t
   }
 }
 
-template <typename T, typename IndexT>
-__global__ void __launch_bounds__(kTopkThreads)
+// THREADS: 1024 or 256.  COPIES: histogram copies, indexed by lane & (COPIES - 1): 32 make a warp's
+// adds conflict-free, 8 keep the histogram at 8 KB for the small blocks (at most 4 lanes per word).
+template <typename T, typename IndexT, int THREADS, int COPIES>
+__global__ void __launch_bounds__(THREADS)
 topk_kernel(const T* __restrict__ scores, int n, int k, IndexT* __restrict__ indices,
             T* __restrict__ values) {
+  static_assert(THREADS >= 256 && THREADS <= 1024 && THREADS % 32 == 0, "256 bins need 256 threads; one warp scans the warp totals");
+  constexpr int kTopkThreads = THREADS;  // shadows the namespace constant inside the kernel
+  constexpr int kWarps = THREADS / 32;
   namespace cg = cooperative_groups;
   cg::cluster_group cluster = cg::this_cluster();
   const int n_ranks = (int)cluster.num_blocks(), rank = (int)cluster.block_rank();
-  // One histogram per lane: hist[bin * 32 + lane].  A warp's 32 adds then touch 32 different
-  // banks and never the same word, however skewed the scores are.
-  __shared__ int hist[256 * 32];
+  // One histogram per lane (COPIES = 32): hist[bin * 32 + lane].  A warp's 32 adds then touch 32
+  // different banks and never the same word, however skewed the scores are.
+  __shared__ int hist[256 * COPIES];
   __shared__ int bin_total[256];     // this CTA's slice, read by the other CTAs of the cluster
   __shared__ uint32_t slice_cnt[2];  // elements above / equal to the threshold in this CTA's slice
   __shared__ uint32_t s_prefix, s_want;
@@ -102,7 +108,7 @@ topk_kernel(const T* __restrict__ scores, int n, int k, IndexT* __restrict__ ind
   uint32_t prefix = 0, mask = 0, want = (uint32_t)k;
   for (int shift = TopkKey<T>::kBits - 8; shift >= 0; shift -= 8) {
 #pragma unroll
-    for (int j = 0; j < 256 * 32 / kTopkThreads; ++j) hist[j * kTopkThreads + tid] = 0;
+    for (int j = 0; j < 256 * COPIES / kTopkThreads; ++j) hist[j * kTopkThreads + tid] = 0;
     __syncthreads();
     for (int c0 = lo; c0 < hi; c0 += kStep) {
       const int i0 = c0 + tid * kTopkItems;
@@ -111,7 +117,7 @@ topk_kernel(const T* __restrict__ scores, int n, int k, IndexT* __restrict__ ind
 #pragma unroll
       for (int j = 0; j < kTopkItems; ++j) {
         if (i0 + j < hi && (key[j] & mask) == prefix)
-          atomicAdd(&hist[((key[j] >> shift) & 255u) * 32 + lane], 1);
+          atomicAdd(&hist[((key[j] >> shift) & 255u) * COPIES + (lane & (COPIES - 1))], 1);
       }
     }
     __syncthreads();
@@ -119,7 +125,7 @@ topk_kernel(const T* __restrict__ scores, int n, int k, IndexT* __restrict__ ind
     if (tid < 256) {
       int total = 0;
 #pragma unroll
-      for (int j = 0; j < 32; ++j) total += hist[tid * 32 + ((j + lane) & 31)];
+      for (int j = 0; j < COPIES; ++j) total += hist[tid * COPIES + ((j + lane) & (COPIES - 1))];
       bin_total[tid] = total;
     }
     cluster.sync();  // every slice's totals are complete (also a barrier of this CTA)
@@ -219,14 +225,14 @@ topk_kernel(const T* __restrict__ scores, int n, int k, IndexT* __restrict__ ind
     if (lane == 31) warp_tot[warp] = incl;
     __syncthreads();
     if (warp == 0) {
-      const uint32_t w = warp_tot[lane];
+      const uint32_t w = lane < kWarps ? warp_tot[lane] : 0u;
       uint32_t wi = w;
 #pragma unroll
       for (int d = 1; d < 32; d <<= 1) {
         const uint32_t up = __shfl_up_sync(0xffffffffu, wi, d);
         if (lane >= d) wi += up;
       }
-      warp_tot[lane] = wi - w;  // exclusive
+      if (lane < kWarps) warp_tot[lane] = wi - w;  // exclusive
       if (lane == 31) chunk_tot = wi;
     }
     __syncthreads();

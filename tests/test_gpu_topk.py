@@ -33,7 +33,8 @@ def _check(scores_cpu: torch.Tensor, k: int):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("rows,n,k", [(1, 1, 1), (3, 100, 7), (5, 4096, 4096), (2, 5000, 1), (4, 70001, 2500),
-                                      (300, 1027, 257), (3, 200003, 50000), (16, 131072, 1000), (40, 65536, 65536)])
+                                      (300, 1027, 257), (3, 200003, 50000), (16, 131072, 1000), (40, 65536, 65536),
+                                      (600, 576, 144), (1000, 2048, 2048), (400, 4096, 1), (2000, 9, 3)])
 def test_matches_torch_topk(dtype, rows, n, k):
     g = torch.Generator().manual_seed(rows * 31 + n + k)
     _check(torch.rand(rows, n, generator=g).to(dtype), k)  # 16-bit dtypes: many exact ties
