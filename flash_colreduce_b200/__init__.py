@@ -6,9 +6,9 @@ and ``__version__``.
 """
 from .dense import naive_colreduce
 from .host import flash_colreduce_host
-from .op import colreduce_partial, finalize_scores, flash_colreduce, flash_colreduce_topk, topk_columns, valid_scores
+from .op import colreduce_partial, finalize_scores, flash_colreduce, flash_colreduce_topk, select_columns, topk_columns, valid_scores
 
 __version__ = "0.1.0"
 __all__ = ["flash_colreduce", "naive_colreduce", "colreduce_partial", "finalize_scores", "valid_scores",
-           "flash_colreduce_host", "topk_columns", "flash_colreduce_topk",
+           "flash_colreduce_host", "topk_columns", "flash_colreduce_topk", "select_columns",
            "__version__"]

@@ -31,6 +31,7 @@ EXPORTS = (
     "fcr_colreduce_static",
     "fcr_finalize",
     "fcr_topk",
+    "fcr_select_above",
     "fcr_read_device_status",
     "fcr_trace_enable",
     "fcr_trace_count",
@@ -105,6 +106,9 @@ def _load() -> C.CDLL:
     lib.fcr_topk.argtypes = [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_int32,
                              C.c_void_p, C.c_void_p]
     lib.fcr_topk.restype = C.c_int
+    lib.fcr_select_above.argtypes = [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_float, C.c_void_p, C.c_int32,
+                                     C.c_void_p, C.c_void_p]
+    lib.fcr_select_above.restype = C.c_int
     lib.fcr_read_device_status.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(C.c_int32)]
     lib.fcr_read_device_status.restype = C.c_int
     lib.fcr_trace_enable.argtypes = [C.c_int32]

@@ -1200,6 +1200,20 @@ static int launch_topk(const void* scores, int rows, int n, int k, void* indices
   return launch_topk_t<T, int>(scores, rows, n, k, indices, values, cluster, 2 * sms, stream);
 }
 
+template <typename T>
+static int launch_select(const void* scores, int rows, int n, float threshold, void* indices,
+                         int index_bits, int* counts, cudaStream_t stream) {
+  if (index_bits == 64)
+    select_above_kernel<T, long long><<<rows, kTopkThreads, 0, stream>>>(
+        static_cast<const T*>(scores), n, threshold, static_cast<long long*>(indices), counts);
+  else
+    select_above_kernel<T, int><<<rows, kTopkThreads, 0, stream>>>(
+        static_cast<const T*>(scores), n, threshold, static_cast<int*>(indices), counts);
+  const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "select_above launch");
+  return FCR_OK;
+}
+
 }  // namespace fcr
 
 using namespace fcr;
@@ -1551,6 +1565,21 @@ int fcr_topk(const void* scores, int32_t dtype, int32_t rows, int32_t n, int32_t
     case FCR_F16: return launch_topk<__half>(scores, rows, n, k, indices, index_bits, values, stream);
     case FCR_BF16: return launch_topk<__nv_bfloat16>(scores, rows, n, k, indices, index_bits, values, stream);
     case FCR_F32: return launch_topk<float>(scores, rows, n, k, indices, index_bits, values, stream);
+    default: return fail(FCR_ERR_BAD_ARG, "invalid dtype");
+  }
+}
+
+int fcr_select_above(const void* scores, int32_t dtype, int32_t rows, int32_t n, float threshold,
+                     void* indices, int32_t index_bits, int32_t* counts, void* stream_v) {
+  if (!scores || !indices || !counts) return fail(FCR_ERR_BAD_ARG, "null scores, indices or counts");
+  if (rows <= 0 || n <= 0) return fail(FCR_ERR_BAD_ARG, "rows and n must be positive");
+  if (index_bits != 32 && index_bits != 64) return fail(FCR_ERR_BAD_ARG, "index_bits must be 32 or 64");
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
+  switch (dtype) {
+    case FCR_F16: return launch_select<__half>(scores, rows, n, threshold, indices, index_bits, counts, stream);
+    case FCR_BF16:
+      return launch_select<__nv_bfloat16>(scores, rows, n, threshold, indices, index_bits, counts, stream);
+    case FCR_F32: return launch_select<float>(scores, rows, n, threshold, indices, index_bits, counts, stream);
     default: return fail(FCR_ERR_BAD_ARG, "invalid dtype");
   }
 }

@@ -257,4 +257,63 @@ topk_kernel(const T* __restrict__ scores, int n, int k, IndexT* __restrict__ ind
   cluster.sync();  // no CTA leaves while another may still read its shared memory
 }
 
+__device__ __forceinline__ float topk_to_float(float v) { return v; }
+__device__ __forceinline__ float topk_to_float(__half v) { return __half2float(v); }
+__device__ __forceinline__ float topk_to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+// Threshold selection: per row the positions whose score is greater than `threshold`, in
+// ascending order, and how many there are.  One CTA per row, one sweep, same block-wide scan as
+// the compaction above.  `indices` holds n entries per row; those beyond the row's count are
+// left untouched.
+template <typename T, typename IndexT>
+__global__ void __launch_bounds__(kTopkThreads)
+select_above_kernel(const T* __restrict__ scores, int n, float threshold, IndexT* __restrict__ indices,
+                    int* __restrict__ counts) {
+  __shared__ uint32_t warp_tot[kTopkThreads / 32];
+  __shared__ uint32_t chunk_tot;
+  const T* row = scores + (size_t)blockIdx.x * n;
+  IndexT* out_idx = indices + (size_t)blockIdx.x * n;
+  const int tid = (int)threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  constexpr int kStep = kTopkThreads * kTopkItems;
+  uint32_t base = 0;
+  for (int c0 = 0; c0 < n; c0 += kStep) {
+    const int i0 = c0 + tid * kTopkItems;
+    bool sel[kTopkItems];
+    uint32_t g = 0;
+#pragma unroll
+    for (int j = 0; j < kTopkItems; ++j) {
+      sel[j] = i0 + j < n && topk_to_float(row[i0 + j]) > threshold;
+      g += sel[j];
+    }
+    uint32_t incl = g;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const uint32_t up = __shfl_up_sync(0xffffffffu, incl, d);
+      if (lane >= d) incl += up;
+    }
+    if (lane == 31) warp_tot[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+      const uint32_t w = warp_tot[lane];
+      uint32_t wi = w;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const uint32_t up = __shfl_up_sync(0xffffffffu, wi, d);
+        if (lane >= d) wi += up;
+      }
+      warp_tot[lane] = wi - w;  // exclusive
+      if (lane == 31) chunk_tot = wi;
+    }
+    __syncthreads();
+    uint32_t pos = base + warp_tot[warp] + (incl - g);
+#pragma unroll
+    for (int j = 0; j < kTopkItems; ++j) {
+      if (sel[j]) out_idx[pos++] = (IndexT)(i0 + j);
+    }
+    base += chunk_tot;
+    __syncthreads();  // warp_tot / chunk_tot are rewritten by the next step
+  }
+  if (tid == 0) counts[blockIdx.x] = (int)base;
+}
+
 }  // namespace fcr

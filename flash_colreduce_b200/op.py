@@ -17,7 +17,7 @@ import torch
 from . import _native as nat
 
 __all__ = ["flash_colreduce", "colreduce_partial", "finalize_scores", "valid_scores", "topk_columns",
-           "flash_colreduce_topk"]
+           "flash_colreduce_topk", "select_columns"]
 
 _DTYPE_CODES = {torch.float16: nat.FCR_F16, torch.bfloat16: nat.FCR_BF16, torch.float32: nat.FCR_F32}
 
@@ -219,6 +219,31 @@ def topk_columns(scores: torch.Tensor, k: int, return_values: bool = True):
                                   indices.data_ptr(), 64, values.data_ptr() if return_values else None, stream)
             nat.check(rc, "fcr_topk")
     return (values.view(*lead, k) if return_values else None), indices.view(*lead, k)
+
+
+def select_columns(scores: torch.Tensor, threshold: float):
+    """Key positions whose score exceeds ``threshold``, per (batch, head) row of ``scores`` (..., N).
+
+    Returns ``(indices, counts)``: ``indices`` (..., N) int64 holds, for every row, the selected
+    positions in ascending order in its first ``counts[...]`` entries (the rest is unspecified), ``counts``
+    (...) int32.  One kernel launch on the current stream; the reference has no counterpart.
+    """
+    if not scores.is_cuda:
+        raise ValueError("scores must be on a CUDA device.")
+    if scores.dtype not in _DTYPE_CODES:
+        raise TypeError(f"select_columns takes fp16, bf16 or fp32 scores; got {scores.dtype}.")
+    n = scores.shape[-1]
+    flat = scores.contiguous().view(-1, n)
+    lead = scores.shape[:-1]
+    indices = torch.empty((flat.shape[0], n), dtype=torch.int64, device=scores.device)
+    counts = torch.zeros((flat.shape[0],), dtype=torch.int32, device=scores.device)
+    if flat.numel() > 0:
+        with torch.cuda.device(scores.device):
+            stream = torch.cuda.current_stream(scores.device).cuda_stream
+            rc = nat.lib.fcr_select_above(flat.data_ptr(), _DTYPE_CODES[scores.dtype], flat.shape[0], n, float(threshold),
+                                          indices.data_ptr(), 64, counts.data_ptr(), stream)
+            nat.check(rc, "fcr_select_above")
+    return indices.view(*lead, n), counts.view(*lead)
 
 
 def flash_colreduce_topk(query: torch.Tensor, key: torch.Tensor, reduction: str, k: int, is_causal: bool = False,

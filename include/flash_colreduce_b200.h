@@ -255,6 +255,17 @@ int fcr_topk(const void* scores, int32_t dtype, int32_t rows, int32_t n, int32_t
              int32_t index_bits, void* values, void* stream);
 
 /*
+ * Row-wise threshold selection over the same kind of array: for every row the
+ * positions whose score is greater than `threshold` (compared in fp32), in
+ * ascending order, into `indices` (rows, n) -- only the first counts[row]
+ * entries of a row are written -- and their number into `counts` (rows).
+ * The other selection rule of a pruning consumer; no counterpart in the
+ * reference.  One launch on `stream`, no workspace, no host synchronisation.
+ */
+int fcr_select_above(const void* scores, int32_t dtype, int32_t rows, int32_t n, float threshold,
+                     void* indices, int32_t index_bits, int32_t* counts, void* stream);
+
+/*
  * Measurement helper: runs a register-only ex2.approx.ftz.f32 loop on every
  * SM and returns the sustained rate in exponentials per second (the MUFU
  * bound of the roofline).  Synchronises the device.  Returns 0 on error.

@@ -72,3 +72,20 @@ def test_on_the_scores_of_the_operator_and_argument_checks():
         topk_columns(scores.double(), 3)
     with pytest.raises(ValueError, match="CUDA"):
         topk_columns(scores.cpu(), 3)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("rows,n", [(1, 1), (3, 100), (7, 8192), (2, 70001), (500, 600)])
+def test_threshold_selection(dtype, rows, n):
+    from flash_colreduce_b200 import select_columns
+
+    g = torch.Generator().manual_seed(rows + n)
+    s = torch.rand(rows, n, generator=g).to(dtype)
+    for thr in (-1.0, 0.25, 0.9, 2.0):
+        idx, cnt = select_columns(s.to(_dev()), thr)
+        idx, cnt = idx.cpu(), cnt.cpu()
+        assert idx.shape == (rows, n) and cnt.shape == (rows,)
+        for r in range(min(rows, 8)):
+            want = (s[r].float() > thr).nonzero().flatten()
+            assert cnt[r].item() == want.numel()
+            assert torch.equal(idx[r, : want.numel()], want)
