@@ -419,6 +419,28 @@ def test_capturable_in_a_cuda_graph():
     assert not torch.equal(captured, eager)
 
 
+def test_decode_and_selection_capturable_in_a_cuda_graph():
+    """Same for a decode shape (key-streaming kernels, score cache) followed by the top-k selection."""
+    from flash_colreduce_b200 import flash_colreduce_topk
+
+    dev = _dev()
+    q, k = _rand((1, 6, 4, 64), 43).to(dev), _rand((1, 6, 2000, 64), 44).to(dev)
+    os.environ["FCR_DEBUG_SYNC"] = "0"
+    try:
+        flash_colreduce_topk(q, k, "sum", 100, is_causal=True)  # one-time kernel set-up outside the capture
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            vals, idx = flash_colreduce_topk(q, k, "sum", 100, is_causal=True)
+        q.copy_(_rand((1, 6, 4, 64), 45).to(dev))
+        graph.replay()
+        torch.cuda.synchronize()
+    finally:
+        os.environ["FCR_DEBUG_SYNC"] = "1"
+    want_vals, want_idx = flash_colreduce_topk(q, k, "sum", 100, is_causal=True)
+    assert torch.equal(idx, want_idx) and torch.equal(vals, want_vals)
+
+
 def test_host_resident_inputs():
     """flash_colreduce_host streams head groups through the GPU; result equals the device API's."""
     from flash_colreduce_b200 import flash_colreduce, flash_colreduce_host
