@@ -1200,15 +1200,29 @@ static int launch_topk(const void* scores, int rows, int n, int k, void* indices
   return launch_topk_t<T, int>(scores, rows, n, k, indices, values, cluster, 2 * sms, stream);
 }
 
+template <typename T, typename IndexT>
+static void launch_select_t(const void* scores, int rows, int n, float threshold, void* indices, int* counts,
+                            bool small, cudaStream_t stream) {
+  if (small)
+    select_above_kernel<T, IndexT, kTopkThreadsSmall><<<rows, kTopkThreadsSmall, 0, stream>>>(
+        static_cast<const T*>(scores), n, threshold, static_cast<IndexT*>(indices), counts);
+  else
+    select_above_kernel<T, IndexT, kTopkThreads><<<rows, kTopkThreads, 0, stream>>>(
+        static_cast<const T*>(scores), n, threshold, static_cast<IndexT*>(indices), counts);
+}
+
 template <typename T>
 static int launch_select(const void* scores, int rows, int n, float threshold, void* indices,
                          int index_bits, int* counts, cudaStream_t stream) {
+  int sms = 0;
+  const int rc = device_sm_count(&sms);
+  if (rc != FCR_OK) return rc;
+  // many short rows: 256-thread blocks, several rows per SM at a time (as for the top-k)
+  const bool small = n <= 16 * kTopkThreadsSmall * kTopkItems && rows >= 2 * sms;
   if (index_bits == 64)
-    select_above_kernel<T, long long><<<rows, kTopkThreads, 0, stream>>>(
-        static_cast<const T*>(scores), n, threshold, static_cast<long long*>(indices), counts);
+    launch_select_t<T, long long>(scores, rows, n, threshold, indices, counts, small, stream);
   else
-    select_above_kernel<T, int><<<rows, kTopkThreads, 0, stream>>>(
-        static_cast<const T*>(scores), n, threshold, static_cast<int*>(indices), counts);
+    launch_select_t<T, int>(scores, rows, n, threshold, indices, counts, small, stream);
   const cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "select_above launch");
   return FCR_OK;

@@ -265,10 +265,12 @@ __device__ __forceinline__ float topk_to_float(__nv_bfloat16 v) { return __bfloa
 // ascending order, and how many there are.  One CTA per row, one sweep, same block-wide scan as
 // the compaction above.  `indices` holds n entries per row; those beyond the row's count are
 // left untouched.
-template <typename T, typename IndexT>
-__global__ void __launch_bounds__(kTopkThreads)
+template <typename T, typename IndexT, int THREADS>
+__global__ void __launch_bounds__(THREADS)
 select_above_kernel(const T* __restrict__ scores, int n, float threshold, IndexT* __restrict__ indices,
                     int* __restrict__ counts) {
+  constexpr int kTopkThreads = THREADS;  // shadows the namespace constant inside the kernel
+  constexpr int kWarps = THREADS / 32;
   __shared__ uint32_t warp_tot[kTopkThreads / 32];
   __shared__ uint32_t chunk_tot;
   const T* row = scores + (size_t)blockIdx.x * n;
@@ -294,14 +296,14 @@ select_above_kernel(const T* __restrict__ scores, int n, float threshold, IndexT
     if (lane == 31) warp_tot[warp] = incl;
     __syncthreads();
     if (warp == 0) {
-      const uint32_t w = warp_tot[lane];
+      const uint32_t w = lane < kWarps ? warp_tot[lane] : 0u;
       uint32_t wi = w;
 #pragma unroll
       for (int d = 1; d < 32; d <<= 1) {
         const uint32_t up = __shfl_up_sync(0xffffffffu, wi, d);
         if (lane >= d) wi += up;
       }
-      warp_tot[lane] = wi - w;  // exclusive
+      if (lane < kWarps) warp_tot[lane] = wi - w;  // exclusive
       if (lane == 31) chunk_tot = wi;
     }
     __syncthreads();
