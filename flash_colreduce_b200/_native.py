@@ -36,8 +36,10 @@ EXPORTS = (
     "fcr_trace_enable",
     "fcr_trace_count",
     "fcr_trace_read",
-    "fcr_debug_scores",
-    "fcr_probe_ex2_rate",
+    "fcr_read_device_status_static",
+    "fcr_poll_device_status",
+    "fcr_launch_count",
+    "fcr_self_test_hooks",
 )
 
 
@@ -117,11 +119,14 @@ def _load() -> C.CDLL:
     lib.fcr_trace_count.restype = C.c_int32
     lib.fcr_trace_read.argtypes = [C.c_int32, C.POINTER(C.c_float), C.POINTER(C.c_float)]
     lib.fcr_trace_read.restype = C.c_int
-    lib.fcr_debug_scores.argtypes = [C.POINTER(Problem), C.c_void_p, C.c_void_p, C.c_void_p,
-                                     C.c_void_p, C.c_size_t, C.c_void_p]
-    lib.fcr_debug_scores.restype = C.c_int
-    lib.fcr_probe_ex2_rate.argtypes = [C.c_int32]
-    lib.fcr_probe_ex2_rate.restype = C.c_double
+    lib.fcr_read_device_status_static.argtypes = [C.c_void_p, C.POINTER(C.c_int32)]
+    lib.fcr_read_device_status_static.restype = C.c_int
+    lib.fcr_poll_device_status.argtypes = [C.POINTER(C.c_int32)]
+    lib.fcr_poll_device_status.restype = C.c_int
+    lib.fcr_launch_count.argtypes = []
+    lib.fcr_launch_count.restype = C.c_int64
+    lib.fcr_self_test_hooks.argtypes = [C.c_int64, C.c_int32]
+    lib.fcr_self_test_hooks.restype = C.c_int
     return lib
 
 

@@ -19,7 +19,19 @@ LIB_NAME = "libflash_colreduce_b200.so"
 LIB_PATH = os.path.join(LIB_DIR, LIB_NAME)
 
 SOURCES = ["colreduce_sm100.cu"]
-HEADERS = ["ptx_sm100.cuh", "softmax_fold.cuh", "plan.h", os.path.join("..", "..", "include", "flash_colreduce_b200.h")]
+# the benchmark's measurement helper, a library of its own (not part of the operator)
+PROBE_NAME = "libfcr_ex2_probe.so"
+PROBE_PATH = os.path.join(LIB_DIR, PROBE_NAME)
+PROBE_SOURCES = ["ex2_probe.cu"]
+
+
+def _dependencies() -> list:
+    """Every file the library is compiled from: all of csrc/ and the public headers."""
+    import glob
+
+    return sorted(glob.glob(os.path.join(CSRC, "*.cu")) + glob.glob(os.path.join(CSRC, "*.cuh")) +
+                  glob.glob(os.path.join(CSRC, "*.h")) +
+                  glob.glob(os.path.join(PKG_DIR, "..", "include", "*.h")))
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -36,11 +48,10 @@ def _nvcc() -> str:
 
 
 def is_stale() -> bool:
-    if not os.path.exists(LIB_PATH):
+    if not os.path.exists(LIB_PATH) or not os.path.exists(PROBE_PATH):
         return True
-    built = os.path.getmtime(LIB_PATH)
-    deps = [os.path.join(CSRC, s) for s in SOURCES + HEADERS]
-    return any(os.path.getmtime(d) > built for d in deps if os.path.exists(d))
+    built = min(os.path.getmtime(LIB_PATH), os.path.getmtime(PROBE_PATH))
+    return any(os.path.getmtime(d) > built for d in _dependencies())
 
 
 def build(force: bool = False, verbose: bool = False) -> str:
@@ -48,16 +59,18 @@ def build(force: bool = False, verbose: bool = False) -> str:
     if not force and not is_stale():
         return LIB_PATH
     os.makedirs(LIB_DIR, exist_ok=True)
-    cmd = [_nvcc(), *NVCC_FLAGS]
-    cmd += os.environ.get("FCR_NVCC_EXTRA", "").split()  # tuning builds, e.g. -DFCR_CHUNK=32
-    if verbose:
-        cmd += ["-Xptxas", "-v"]
-    cmd += ["-o", LIB_PATH] + [os.path.join(CSRC, s) for s in SOURCES]
-    proc = subprocess.run(cmd, capture_output=True, text=True)
-    if verbose or proc.returncode != 0:
-        sys.stderr.write(proc.stdout + proc.stderr)
-    if proc.returncode != 0:
-        raise RuntimeError("nvcc failed building " + LIB_NAME)
+    for target, sources in ((LIB_PATH, SOURCES), (PROBE_PATH, PROBE_SOURCES)):
+        cmd = [_nvcc(), *NVCC_FLAGS]
+        if target == LIB_PATH:
+            cmd += os.environ.get("FCR_NVCC_EXTRA", "").split()  # tuning builds, e.g. -DFCR_POLY=3
+        if verbose:
+            cmd += ["-Xptxas", "-v"]
+        cmd += ["-o", target] + [os.path.join(CSRC, s) for s in sources]
+        proc = subprocess.run(cmd, capture_output=True, text=True)
+        if verbose or proc.returncode != 0:
+            sys.stderr.write(proc.stdout + proc.stderr)
+        if proc.returncode != 0:
+            raise RuntimeError("nvcc failed building " + os.path.basename(target))
     return LIB_PATH
 
 

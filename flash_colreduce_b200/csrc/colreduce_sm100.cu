@@ -15,9 +15,11 @@
 //       No atomics and no cross-thread reduction; splits of the query range
 //       go to a partial buffer that a last kernel combines in fixed order.
 //
-// Warp roles inside a CTA (320 threads): warps 0-3 and 4-7 are the two softmax
-// warpgroups (one per stationary tile), warp 8 issues TMA loads, warp 9 issues
-// tcgen05.mma and owns the tensor-memory allocation.
+// Warp roles inside a CTA (608 threads, one CTA per SM): warps 0-15 are the
+// softmax warps (two warpgroups of four warps per stationary tile, each folding
+// every other accumulator tile of it), warp 16 issues the TMA loads and hands
+// out work items, warps 17 and 18 issue tcgen05.mma (one per stationary tile;
+// warp 17 also owns the tensor-memory allocation).
 //
 // The arithmetic follows the reference kernel: scores are scaled by
 // scale/ln(2) and exponentials are base 2 (flash_colreduce/flash.py:59-78,
@@ -46,7 +48,7 @@
 
 namespace fcr {
 
-enum { PH_DUMP = 0, PH_ROWS = 1, PH_COLS = 2 };
+enum { PH_ROWS = 1, PH_COLS = 2 };
 
 #ifndef FCR_COLSPLIT
 #define FCR_COLSPLIT 2
@@ -84,7 +86,7 @@ constexpr int kChunkRows = FCR_CHUNK_ROWS;
 constexpr int kChunkCols = FCR_CHUNK_COLS;
 static_assert(kSpan % kChunkRows == 0 && kChunkRows % 32 == 0 && kSpan % kChunkCols == 0 &&
                   kChunkCols % 32 == 0, "chunk must divide the per-thread span");
-constexpr long long kWaitLimitCycles = 2000000000LL;  // about one second
+constexpr long long kWaitLimitCycles = 2000000000LL;  // default bound of a device-side wait: about one second
 
 // Device status codes (status word 0).  Word 1: block, word 2: thread, word 3: detail.
 enum {
@@ -116,16 +118,38 @@ struct PassParams : PassGeom {
   float* part_m;   // [n_split][BH][m_pad]
   float* part_l;   // [n_split][BH][m_pad]
   float* part_out; // [n_split][BH][n_pad]
-  float* dump;     // [BH][m_pad][n_pad] (PH_DUMP); [BH][M][n_pad] score cache of the key-streaming rows pass
+  float* dump;     // [BH][M][n_pad] score cache of the key-streaming rows pass (null: none)
   void* out;       // [BH][N] of out_dtype
   int out_dtype;
   int mean_mode;   // 0: none, 1: divide by div_M, 2: causal rule
   int div_M, div_N, div_c;
   int* status;
+  int* host_status;       // the device's status mailbox in mapped host memory (null: none)
+  long long wait_limit;   // bound of every device-side wait, in clock64 cycles
+  int skip_ring_load;     // self-test: CTA 0's TMA warp leaves out this ring load (-1: none)
   int* sched_counter;  // zero at launch; hands out work items beyond the first gridDim.x
   int key_tiles;       // key-streaming kernels: 128-key tiles per head
   int fold_cols;       // key-streaming columns pass: M rounded up to a 32-query chunk
 };
+
+// First failure wins: the code goes to status word 0 of the workspace and, when the device has
+// one, to the mailbox in mapped host memory, where the host sees it without a synchronisation.
+__device__ __noinline__ void report_status(const PassParams& p, int code, int detail) {
+  if (atomicCAS(p.status, 0, code) == 0) {
+    p.status[1] = (int)blockIdx.x;
+    p.status[2] = (int)threadIdx.x;
+    p.status[3] = detail;
+    if (p.host_status != nullptr) {
+      volatile int* hs = p.host_status;
+      hs[1] = (int)blockIdx.x;
+      hs[2] = (int)threadIdx.x;
+      hs[3] = detail;
+      __threadfence_system();
+      hs[0] = code;
+    }
+    __threadfence_system();
+  }
+}
 
 // SHORT selects the buffering for work items that stream only a few tiles: two stationary
 // stages, so that the next item's stationary tiles are fetched while this one is computed,
@@ -163,29 +187,20 @@ struct SmemLayout {
   static_assert(kDynamicBytes <= 232448, "exceeds the 227 KB shared memory of an sm_100 CTA");
 };
 
-__device__ __noinline__ void report_status(int* status, int code, int detail) {
-  if (atomicCAS(status, 0, code) == 0) {
-    status[1] = (int)blockIdx.x;
-    status[2] = (int)threadIdx.x;
-    status[3] = detail;
-    __threadfence();
-  }
-}
-
 // Bounded mbarrier wait.  Returns false when the wait limit expired here or in
 // another thread of the CTA (the abort flag); the caller then leaves its loop.
 __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                         int* status, int code) {
+                                         const PassParams& p, int code) {
   if (ptx::mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   uint32_t spins = 0;
   while (true) {
     if (ptx::mbar_try_wait(bar, parity)) return true;
-    if ((++spins & 63u) == 0) {
+    if ((++spins & 7u) == 0) {
       if (*abort_flag) return false;
-      if (clock64() - t0 > kWaitLimitCycles) {
+      if (clock64() - t0 > p.wait_limit) {
         *abort_flag = 1;
-        report_status(status, code, (int)parity);
+        report_status(p, code, (int)parity);
         return false;
       }
     }
@@ -193,31 +208,10 @@ __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile
 }
 // Same, with a warp-uniform result so that .sync.aligned instructions that
 // follow are executed by all 32 lanes or by none.
-#ifdef FCR_PROFILE
-// Tuning builds only: cycles spent in each kind of wait, summed over lane 0 of
-// every warp, accumulated in shared memory and flushed to status words 16+.
-__shared__ unsigned long long g_prof[40];
-#endif
-#ifdef FCR_PROFILE
-#define PROF_T0() const long long prof_t = clock64()
-#define PROF_ADD(code) prof_acc[(code) % 10] += clock64() - prof_t
-#define PROF_DECL() long long prof_acc[10] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0}
-#define PROF_FLUSH(base)                                                              \
-  if ((threadIdx.x & 31) == 0) {                                                      \
-    _Pragma("unroll") for (int i_ = 0; i_ < 10; ++i_)                                 \
-        atomicAdd(&g_prof[(base) + i_], (unsigned long long)prof_acc[i_]);            \
-  }
-#define WAIT(bar, par, code) ([&]() { PROF_T0(); const bool ok_ = wait_bar_warp(bar, par, abort_flag, p.status, code); PROF_ADD(code); return ok_; }())
-#else
-#define PROF_T0()
-#define PROF_ADD(code)
-#define PROF_DECL()
-#define PROF_FLUSH(base)
-#define WAIT(bar, par, code) wait_bar_warp(bar, par, abort_flag, p.status, code)
-#endif
+#define WAIT(bar, par, code) wait_bar_warp(bar, par, abort_flag, p, code)
 __device__ __forceinline__ bool wait_bar_warp(uint32_t bar, uint32_t parity,
-                                              volatile int* abort_flag, int* status, int code) {
-  const bool ok = wait_bar(bar, parity, abort_flag, status, code);
+                                              volatile int* abort_flag, const PassParams& p, int code) {
+  const bool ok = wait_bar(bar, parity, abort_flag, p, code);
   return __all_sync(0xffffffffu, ok);
 }
 
@@ -247,7 +241,7 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
   extern __shared__ __align__(1024) uint8_t smem[];
   const uint32_t base = ptx::smem_u32(smem);
   if ((base & 1023u) != 0) {
-    if (threadIdx.x == 0) report_status(p.status, ST_SMEM_MISALIGNED, (int)base);
+    if (threadIdx.x == 0) report_status(p, ST_SMEM_MISALIGNED, (int)base);
     return;
   }
 
@@ -298,12 +292,6 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
 
   const int warp = (int)(threadIdx.x >> 5);
   const int lane = (int)(threadIdx.x & 31);
-#ifdef FCR_PROFILE
-  if (threadIdx.x < 40) g_prof[threadIdx.x] = 0;
-  const long long prof_t0 = clock64();
-  unsigned long long prof_g0;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(prof_g0));
-#endif
 
   if (warp == 0) {  // the lanes of one warp initialise the barriers side by side
     if (lane < KS) {
@@ -351,7 +339,6 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
 
   if (warp == kProducerWarp) {
     // ------------------------------------------------------------ TMA warp
-    PROF_DECL();
     // Work items are handed out dynamically: the first is the CTA's own index,
     // later ones come from a global counter (fetched one item early, so that the
     // atomic's latency is hidden).  Each item is decoded here once and announced
@@ -436,7 +423,10 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
           const uint32_t s = ring_seq % KR, ph = (ring_seq / KR) & 1u;
           ok = WAIT(bar_ring_empty(s), ph ^ 1u, ST_WAIT_RING_EMPTY);
           if (!ok) break;
-          if (lane == 0) {
+          // self-test of the bounded waits: one load of CTA 0 is never requested (nothing is in
+          // flight for its slot), so the consumers' waits on it run into their limit
+          const bool left_out = blockIdx.x == 0 && (int)ring_seq == p.skip_ring_load;
+          if (lane == 0 && !left_out) {
             ptx::mbar_arrive_expect_tx(bar_ring_full(s), L::kSlotBytes);
 #pragma unroll
             for (int hf = 0; hf < L::kSlotHalves; ++hf)
@@ -462,17 +452,12 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
       }
       g = g_next;
     }
-#ifdef FCR_PROFILE
-    prof_acc[0] = clock64() - prof_t0;
-#endif
-    PROF_FLUSH(10);
   } else if (warp >= kMmaWarp) {
     // ----------------------------------------------------------- MMA warps
     // One issuing warp per stationary sub-tile: tcgen05.mma issue blocks while
     // the tensor pipe's short queue is full, so with a single issuer the pipe
     // drains during that warp's barrier handshakes; with two, one warp's
     // handshakes overlap the other's MMAs.
-    PROF_DECL();
     const int a = (warp - kMmaWarp) % kSubTiles;
     const int my_buf = (warp - kMmaWarp) / kSubTiles;  // only with one issuer per accumulator buffer
     // Accumulator buffer of a tile = (its index within the work item + the item's parity) mod 2,
@@ -511,7 +496,6 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
               if (!ok) break;
             }
             ptx::tc_fence_after_sync();
-            PROF_T0();
             if (lane == 0) {
               const uint32_t d = tmem_base + (uint32_t)(a * 2 + ts) * kTile;
               const uint32_t b_addr = s_ring + s * L::kSlotBytes;
@@ -540,7 +524,6 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
               ptx::umma_commit(bar_ring_empty(s));
             }
             __syncwarp();
-            PROF_ADD(25);
             if (piece + 1 == L::kPieces) {
               if (ts) ++tm_use[1]; else ++tm_use[0];
             }
@@ -561,16 +544,11 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
       const uint32_t last = item_seq - 1;
       WAIT(bar_stat_empty(last % KS), (last / KS) & 1u, ST_WAIT_DRAIN);
     }
-#ifdef FCR_PROFILE
-    prof_acc[0] = clock64() - prof_t0;
-#endif
-    PROF_FLUSH(20);
   } else {
     // -------------------------------------------------------- softmax warps
     // Warp w reads tensor-memory lanes 32*(w%4).. (a hardware rule), belongs to
     // stationary sub-tile a and folds columns [part*kSpan, (part+1)*kSpan) of
     // each of that sub-tile's accumulator tiles.
-    PROF_DECL();
     const int a = (warp >> 2) % kSubTiles;
     const int part = warp / (4 * kSubTiles);
     const int tid_wg = (warp & 3) * 32 + lane;
@@ -637,7 +615,7 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
           const uint32_t taddr =
               tmem_base + lane_field + (uint32_t)(a * 2 + ts) * kTile + (uint32_t)col_base;
           const int c0 = t * kTile + col_base;  // streamed index of this thread's first column
-          const bool need_mask = (PHASE != PH_DUMP) && (t >= mask_from || t < mask_until);
+          const bool need_mask = t >= mask_from || t < mask_until;
           const int lim_lo = valid_lo - c0, lim_hi = valid_hi - c0;
           const float* lse_s =
               reinterpret_cast<const float*>(smem + L::off_lse + sl * L::kLseBytes) + col_base;
@@ -645,14 +623,7 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
           constexpr int kChunk = (PHASE == PH_COLS) ? kChunkCols : kChunkRows;
           uint32_t ra[kChunk];
           auto consume = [&](const uint32_t* r, int c) {
-            if constexpr (PHASE == PH_DUMP) {
-              float4* dst = reinterpret_cast<float4*>(
-                  p.dump + ((size_t)g.bh * p.m_pad + mine) * p.n_pad + c0 + kChunk * c);
-#pragma unroll
-              for (int q = 0; q < kChunk / 4; ++q)
-                dst[q] = make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
-                                     __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
-            } else if constexpr (PHASE == PH_ROWS) {
+            if constexpr (PHASE == PH_ROWS) {
               if (need_mask)
                 rows_chunk<true, kChunk>(r, p.scale2, lim_hi - kChunk * c, m_run, l_run);
               else
@@ -668,22 +639,14 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
           // one chunk at a time: the other warps of the scheduler cover the load latency
 #pragma unroll
           for (int c = 0; c < kSpan / kChunk; ++c) {
-            {
-              PROF_T0();
-              ptx::tmem_ld<kChunk>(taddr + c * kChunk, ra);
-              ptx::tmem_ld_wait<kChunk>(ra);
-              PROF_ADD(33);
-            }
+            ptx::tmem_ld<kChunk>(taddr + c * kChunk, ra);
+            ptx::tmem_ld_wait<kChunk>(ra);
             if (c + 1 == kSpan / kChunk) {
               ptx::tc_fence_before_sync();
               __syncwarp();
               if (lane == 0) ptx::mbar_arrive(bar_tm_empty(a, ts));
             }
-            {
-              PROF_T0();
-              consume(ra, c);
-              PROF_ADD(34);
-            }
+            consume(ra, c);
           }
         }
         if (holds_slot) {
@@ -693,7 +656,7 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
       }
       ring_base += (uint32_t)(g.c_hi - g.c_lo);
       if (!ok) break;
-      if (PHASE == PH_DUMP || g.r0[a] >= p.LS) continue;  // nothing to write for this sub-tile
+      if (g.r0[a] >= p.LS) continue;  // nothing to write for this sub-tile
 
       // ------------------------------------------------------ item epilogue
       // The kColSplit threads that share a row / column combine their partial
@@ -757,10 +720,6 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
         }
       }
     }
-#ifdef FCR_PROFILE
-    prof_acc[0] = clock64() - prof_t0;
-#endif
-    PROF_FLUSH(30);
   }
 
   // ------------------------------------------------------------- teardown
@@ -777,21 +736,6 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
     ptx::tc_fence_after_sync();
     ptx::tmem_dealloc(tmem_base, kTmemCols);
   }
-#ifdef FCR_PROFILE
-  if (threadIdx.x < 40)
-    atomicAdd(reinterpret_cast<unsigned long long*>(p.status + 16) + threadIdx.x +
-                  (PHASE == PH_COLS ? 40 : 0), g_prof[threadIdx.x]);
-  if (threadIdx.x == 0) {
-    // wall-clock span of the CTAs: earliest start, latest end, sum of lifetimes (ns)
-    unsigned long long g1;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g1));
-    unsigned long long* w = reinterpret_cast<unsigned long long*>(p.status + 16) + 80 + (PHASE == PH_COLS ? 4 : 0);
-    atomicMin(w + 0, prof_g0);
-    atomicMax(w + 1, g1);
-    atomicAdd(w + 2, g1 - prof_g0);
-    atomicMax(w + 3, g1 - prof_g0);
-  }
-#endif
 }
 
 }  // namespace fcr
@@ -896,20 +840,6 @@ __global__ void finalize_kernel(const float* __restrict__ acc, PassParams p) {
   }
 }
 
-__global__ void ex2_probe_kernel(float* sink, int iters) {
-  float v[8];
-#pragma unroll
-  for (int u = 0; u < 8; ++u) v[u] = -1.0f - 0.001f * (float)(threadIdx.x + u);
-  for (int it = 0; it < iters; ++it) {
-#pragma unroll
-    for (int u = 0; u < 8; ++u) v[u] = ptx::ex2(v[u]) - 1.5f;
-  }
-  float s = 0.f;
-#pragma unroll
-  for (int u = 0; u < 8; ++u) s += v[u];
-  if (s == 123.456f) sink[0] = s;
-}
-
 // ===================================================================== host
 static thread_local std::string g_last_error;
 
@@ -999,22 +929,92 @@ static int make_tensor_map(CUtensorMap* map, const void* ptr, int dtype, int D, 
   return FCR_OK;
 }
 
-static int device_sm_count(int* out) {
+// Facts about a device and the resources the library keeps on it, looked up once per device.
+struct DeviceInfo {
+  bool ready = false;
+  int index = 0;
+  int sms = 0;
+  // Status mailbox: 16 ints of pinned host memory mapped into the device's address space.  A
+  // kernel whose bounded wait expires writes its status there as well as into the workspace, so
+  // the next library call on the device sees the failure without synchronising anything.
+  int* mailbox_host = nullptr;
+  int* mailbox_dev = nullptr;
+};
+static std::mutex g_dev_mutex;
+static DeviceInfo g_dev[64];
+
+// The current device's entry.  With `want_mailbox` the mailbox is allocated on first use (the
+// only allocation the library ever makes: 64 bytes of pinned host memory per device).
+static int device_info(const DeviceInfo** out, bool want_mailbox) {
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
-  int major = 0, sms = 0;
-  e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
-  if (e != cudaSuccess) return cuda_fail(e, "cudaDeviceGetAttribute");
-  if (major != 10)
-    return fail(FCR_ERR_UNSUPPORTED,
-                "this library contains sm_100a code only; the current device has compute capability major " +
-                    std::to_string(major));
-  e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  if (e != cudaSuccess) return cuda_fail(e, "cudaDeviceGetAttribute");
-  *out = sms;
+  if (dev < 0 || dev >= 64) return fail(FCR_ERR_UNSUPPORTED, "device ordinal beyond 63");
+  DeviceInfo& d = g_dev[dev];
+  std::lock_guard<std::mutex> lock(g_dev_mutex);
+  if (!d.ready) {
+    int major = 0, sms = 0;
+    e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaDeviceGetAttribute");
+    if (major != 10)
+      return fail(FCR_ERR_UNSUPPORTED,
+                  "this library contains sm_100a code only; the current device has compute capability major " +
+                      std::to_string(major));
+    e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaDeviceGetAttribute");
+    d.index = dev;
+    d.sms = sms;
+    d.ready = true;
+  }
+  if (want_mailbox && !d.mailbox_host) {
+    void* h = nullptr;
+    void* dptr = nullptr;
+    e = cudaHostAlloc(&h, 64, cudaHostAllocMapped | cudaHostAllocPortable);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaHostAlloc(status mailbox)");
+    memset(h, 0, 64);
+    e = cudaHostGetDevicePointer(&dptr, h, 0);
+    if (e != cudaSuccess) {
+      cudaFreeHost(h);
+      return cuda_fail(e, "cudaHostGetDevicePointer(status mailbox)");
+    }
+    d.mailbox_dev = reinterpret_cast<int*>(dptr);
+    d.mailbox_host = reinterpret_cast<int*>(h);
+  }
+  *out = &d;
   return FCR_OK;
 }
+
+static int device_sm_count(int* out) {
+  const DeviceInfo* d = nullptr;
+  const int rc = device_info(&d, false);
+  if (rc != FCR_OK) return rc;
+  *out = d->sms;
+  return FCR_OK;
+}
+
+static std::string status_text(const volatile int* w) {
+  return "device status " + std::to_string(w[0]) + " (block " + std::to_string(w[1]) + ", thread " +
+         std::to_string(w[2]) + ", detail " + std::to_string(w[3]) + "): a bounded wait inside a kernel expired";
+}
+
+// A failure a kernel left in the device's mailbox is reported once, by the first library call
+// that looks; the mailbox is then cleared.
+static int check_mailbox(const DeviceInfo& d, int32_t* code_out) {
+  if (code_out) *code_out = 0;
+  volatile int* w = d.mailbox_host;
+  if (!w || w[0] == 0) return FCR_OK;
+  if (code_out) *code_out = w[0];
+  const std::string msg = status_text(w) + " in an earlier call on this device; its output is not valid";
+  w[0] = 0;
+  return fail(FCR_ERR_DEVICE_TIMEOUT, msg);
+}
+
+// Kernel launches made by the library in this process.
+static std::atomic<long long> g_launches{0};
+
+// Overrides for the self-test of the bounded waits (calling thread only).
+static thread_local long long g_wait_limit_override = 0;
+static thread_local int g_skip_ring_load = -1;
 
 static uint32_t instr_desc(int dtype, bool negate_a) {
   // kind::f16 / kind::tf32, fp32 accumulate, both operands K-major, M = 128, N = 128
@@ -1038,8 +1038,12 @@ static cudaError_t launch_kernel(void (*kern)(KArgs...), dim3 grid, dim3 block, 
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = dependent ? 1 : 0;
+  g_launches.fetch_add(1, std::memory_order_relaxed);
   return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
 }
+
+// Device the calling thread's current operator call runs on (set by run_colreduce).
+static thread_local int t_device = 0;
 
 template <int PHASE, int DPAD, int RED, bool SHORT>
 static int launch_pass(const CUtensorMap& stat, const CUtensorMap& strm, const PassParams& pp,
@@ -1048,10 +1052,8 @@ static int launch_pass(const CUtensorMap& stat, const CUtensorMap& strm, const P
   constexpr int smem = SmemLayout<DPAD, SHORT>::kDynamicBytes;
   // the shared-memory opt-in is per kernel and device: do it once for each
   static std::atomic<unsigned long long> opted_in{0};
-  int dev = 0;
-  cudaError_t e = cudaGetDevice(&dev);
-  if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
-  const unsigned long long bit = 1ULL << (dev & 63);
+  cudaError_t e = cudaSuccess;
+  const unsigned long long bit = 1ULL << (t_device & 63);
   if (!(opted_in.load(std::memory_order_acquire) & bit)) {
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute");
@@ -1080,10 +1082,8 @@ static int launch_keystream(const CUtensorMap& map_q, const CUtensorMap& map_k, 
   auto kern = keystream_kernel<PHASE, DPAD, RED>;
   constexpr int smem = KeyStreamSmem<DPAD>::kDynamicBytes;
   static std::atomic<unsigned long long> opted_in{0};
-  int dev = 0;
-  cudaError_t e = cudaGetDevice(&dev);
-  if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
-  const unsigned long long bit = 1ULL << (dev & 63);
+  cudaError_t e = cudaSuccess;
+  const unsigned long long bit = 1ULL << (t_device & 63);
   if (!(opted_in.load(std::memory_order_acquire) & bit)) {
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute");
@@ -1121,7 +1121,7 @@ static int check_workspace(const fcr_plan& pl, const void* ws, size_t ws_bytes) 
 }
 
 static void fill_common(PassParams& pp, const fcr_problem& pr, const fcr_plan& pl, uint8_t* ws,
-                        bool cols) {
+                        bool cols, int* host_status) {
   memset(&pp, 0, sizeof(pp));
   static_cast<PassGeom&>(pp) = pass_geometry(pr, pl, cols);
   pp.m_pad = pl.m_pad;
@@ -1138,6 +1138,9 @@ static void fill_common(PassParams& pp, const fcr_problem& pr, const fcr_plan& p
   pp.part_out = reinterpret_cast<float*>(ws + pl.off_part_out);
   pp.status = reinterpret_cast<int*>(ws + pl.off_status);
   pp.sched_counter = pp.status + (cols ? 9 : 8);
+  pp.host_status = host_status;
+  pp.wait_limit = g_wait_limit_override > 0 ? g_wait_limit_override : kWaitLimitCycles;
+  pp.skip_ring_load = g_skip_ring_load;
 }
 
 static void fill_mean(PassParams& pp, int reduction, int is_causal, int M, int N) {
@@ -1161,11 +1164,13 @@ static int launch_topk_t(const void* scores, int rows, int n, int k, void* indic
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)rows * cluster);
   cfg.blockDim = dim3(kTopkThreads);
+  cfg.stream = stream;  // both launch shapes below go to the caller's stream
   // many short rows: 256-thread blocks, several rows per SM at a time
   const bool small = cluster == 1 && n <= 16 * kTopkThreadsSmall * kTopkItems && rows >= small_rows_from;
   if (small) {
     cfg.blockDim = dim3(kTopkThreadsSmall);
     cfg.numAttrs = 0;
+    g_launches.fetch_add(1, std::memory_order_relaxed);
     cudaError_t es = cudaLaunchKernelEx(&cfg, topk_kernel<T, IndexT, kTopkThreadsSmall, 8>,
                                         static_cast<const T*>(scores), n, k, static_cast<IndexT*>(indices),
                                         static_cast<T*>(values));
@@ -1173,7 +1178,6 @@ static int launch_topk_t(const void* scores, int rows, int n, int k, void* indic
     if (es != cudaSuccess) return cuda_fail(es, "topk launch");
     return FCR_OK;
   }
-  cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = (unsigned)cluster;
@@ -1181,6 +1185,7 @@ static int launch_topk_t(const void* scores, int rows, int n, int k, void* indic
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = cluster > 1 ? 1 : 0;  // a single CTA per row is an ordinary launch
+  g_launches.fetch_add(1, std::memory_order_relaxed);
   cudaError_t e = cudaLaunchKernelEx(&cfg, topk_kernel<T, IndexT, kTopkThreads, 32>, static_cast<const T*>(scores), n, k,
                                      static_cast<IndexT*>(indices), static_cast<T*>(values));
   if (e == cudaSuccess) e = cudaGetLastError();
@@ -1203,6 +1208,7 @@ static int launch_topk(const void* scores, int rows, int n, int k, void* indices
 template <typename T, typename IndexT>
 static void launch_select_t(const void* scores, int rows, int n, float threshold, void* indices, int* counts,
                             bool small, cudaStream_t stream) {
+  g_launches.fetch_add(1, std::memory_order_relaxed);
   if (small)
     select_above_kernel<T, IndexT, kTopkThreadsSmall><<<rows, kTopkThreadsSmall, 0, stream>>>(
         static_cast<const T*>(scores), n, threshold, static_cast<IndexT*>(indices), counts);
@@ -1248,11 +1254,6 @@ int fcr_plan_problem(const fcr_problem* problem, int32_t num_sms, fcr_plan* plan
   std::string err;
   const int rc = plan_problem(*problem, sms, *plan, err);
   if (rc != FCR_OK) return fail(rc, err);
-  // Tuning knob: FCR_HEAD_GROUP overrides how many heads share the L2 cache.
-  if (const char* hg = getenv("FCR_HEAD_GROUP")) {
-    const int v = atoi(hg);
-    if (v >= 1) plan->head_group = std::min(v, problem->B * problem->H);
-  }
   return FCR_OK;
 }
 
@@ -1288,19 +1289,55 @@ size_t fcr_workspace_bytes(const fcr_problem* problem, int32_t num_sms) {
   return (size_t)pl.workspace_bytes;
 }
 
-int fcr_colreduce(const fcr_problem* problem, const void* q, const void* k, void* out,
-                  int32_t out_dtype, void* workspace, size_t workspace_bytes, void* stream_v) {
-  if (!problem || !q || !k || !out) return fail(FCR_ERR_BAD_ARG, "null argument");
-  if (out_dtype != FCR_F16 && out_dtype != FCR_BF16 && out_dtype != FCR_F32)
-    return fail(FCR_ERR_BAD_ARG, "invalid out_dtype");
-  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
+}  // extern "C"
+
+// Plans of the calling thread's recent problems: a repeat call with the same problem struct on
+// the same device plans nothing (the plan depends on the problem and the SM count only).
+struct PlanCacheEntry {
+  fcr_problem problem;
+  int device;
+  fcr_plan plan;
+};
+static bool same_problem(const fcr_problem& a, const fcr_problem& b) {
+  return a.B == b.B && a.H == b.H && a.M == b.M && a.N == b.N && a.D == b.D &&
+         memcmp(a.q_strides, b.q_strides, sizeof(a.q_strides)) == 0 &&
+         memcmp(a.k_strides, b.k_strides, sizeof(a.k_strides)) == 0 && a.in_dtype == b.in_dtype &&
+         a.reduction == b.reduction && a.is_causal == b.is_causal &&
+         memcmp(&a.scale, &b.scale, sizeof(float)) == 0 && a.causal_offset == b.causal_offset &&
+         a.mean_M == b.mean_M && a.mean_N == b.mean_N;
+}
+static int plan_for_call(const fcr_problem& pr, const DeviceInfo& dev, const fcr_plan** out) {
+  constexpr int kEntries = 8;
+  static thread_local PlanCacheEntry cache[kEntries];
+  static thread_local int used = 0, next = 0;
+  for (int i = 0; i < used; ++i)
+    if (cache[i].device == dev.index && same_problem(cache[i].problem, pr)) {
+      *out = &cache[i].plan;
+      return FCR_OK;
+    }
+  std::string err;
   fcr_plan pl;
-  int rc = fcr_plan_problem(problem, 0, &pl);
+  const int rc = plan_problem(pr, dev.sms, pl, err);
+  if (rc != FCR_OK) return fail(rc, err);
+  PlanCacheEntry& e = cache[next];
+  e.problem = pr;
+  e.device = dev.index;
+  e.plan = pl;
+  *out = &e.plan;
+  next = (next + 1) % kEntries;
+  if (used < kEntries) ++used;
+  return FCR_OK;
+}
+
+// The operator proper, behind fcr_colreduce and fcr_colreduce_static.
+static int run_colreduce(const fcr_problem& pr, const fcr_plan& pl, const DeviceInfo& dev, const void* q,
+                         const void* k, void* out, int32_t out_dtype, void* workspace,
+                         size_t workspace_bytes, cudaStream_t stream) {
+  int rc = check_workspace(pl, workspace, workspace_bytes);
   if (rc != FCR_OK) return rc;
-  rc = check_workspace(pl, workspace, workspace_bytes);
-  if (rc != FCR_OK) return rc;
-  const fcr_problem& pr = *problem;
   uint8_t* ws = reinterpret_cast<uint8_t*>(workspace);
+  t_device = dev.index;
+  int* const mailbox = dev.mailbox_dev;
 
   CUtensorMap map_q, map_k;
   rc = make_tensor_map(&map_q, q, pr.in_dtype, pr.D, pr.M, pr.H, pr.B, pr.q_strides);
@@ -1310,20 +1347,13 @@ int fcr_colreduce(const fcr_problem* problem, const void* q, const void* k, void
 
   cudaError_t e = cudaMemsetAsync(ws + pl.off_status, 0, kStatusWords * 4, stream);
   if (e != cudaSuccess) return cuda_fail(e, "cudaMemsetAsync");
-#ifdef FCR_PROFILE
-  {  // the two "earliest start" slots of the tuning counters start at the maximum
-    const unsigned long long big = ~0ULL;
-    cudaMemcpyAsync(ws + pl.off_status + 64 + 80 * 8, &big, 8, cudaMemcpyHostToDevice, stream);
-    cudaMemcpyAsync(ws + pl.off_status + 64 + 84 * 8, &big, 8, cudaMemcpyHostToDevice, stream);
-  }
-#endif
 
   if (pl.key_stream) {
     // Decode shapes: both passes stream the key tiles past the head's one query tile.
     trace_mark(0, stream);
     PassParams pp;
     auto fill = [&](bool cols) {
-      fill_common(pp, pr, pl, ws, cols);
+      fill_common(pp, pr, pl, ws, cols, mailbox);
       pp.n_split = pl.key_chunks;
       pp.n_items = pl.row_items;
       pp.key_tiles = pl.n_pad / kTile;
@@ -1377,7 +1407,7 @@ int fcr_colreduce(const fcr_problem* problem, const void* q, const void* k, void
   // rows pass: Q stationary, K streamed
   trace_mark(0, stream);
   PassParams pp;
-  fill_common(pp, pr, pl, ws, false);
+  fill_common(pp, pr, pl, ws, false, mailbox);
   rc = launch_pass_d<PH_ROWS, RED_SUM>(pl.d_pad, (pl.short_items & 1) != 0, map_q, map_k, pp,
                                        pl.row_ctas, stream);
   if (rc != FCR_OK) return rc;
@@ -1392,7 +1422,7 @@ int fcr_colreduce(const fcr_problem* problem, const void* q, const void* k, void
 
   // columns pass: K stationary, Q streamed
   trace_mark(1, stream);
-  fill_common(pp, pr, pl, ws, true);
+  fill_common(pp, pr, pl, ws, true, mailbox);
   pp.out = out;
   pp.out_dtype = out_dtype;
   fill_mean(pp, pr.reduction, pr.is_causal, pr.mean_M > 0 ? pr.mean_M : pr.M,
@@ -1413,6 +1443,41 @@ int fcr_colreduce(const fcr_problem* problem, const void* q, const void* k, void
     if (e != cudaSuccess) return cuda_fail(e, "final_reduce launch");
   }
   trace_mark(2, stream);
+  return FCR_OK;
+}
+
+extern "C" {
+
+int fcr_colreduce(const fcr_problem* problem, const void* q, const void* k, void* out,
+                  int32_t out_dtype, void* workspace, size_t workspace_bytes, void* stream_v) {
+  if (!problem || !q || !k || !out) return fail(FCR_ERR_BAD_ARG, "null argument");
+  if (out_dtype != FCR_F16 && out_dtype != FCR_BF16 && out_dtype != FCR_F32)
+    return fail(FCR_ERR_BAD_ARG, "invalid out_dtype");
+  const DeviceInfo* dev = nullptr;
+  int rc = device_info(&dev, true);
+  if (rc != FCR_OK) return rc;
+  rc = check_mailbox(*dev, nullptr);  // a wait that expired in an earlier call is reported here
+  if (rc != FCR_OK) return rc;
+  const fcr_plan* pl = nullptr;
+  rc = plan_for_call(*problem, *dev, &pl);
+  if (rc != FCR_OK) return rc;
+  return run_colreduce(*problem, *pl, *dev, q, k, out, out_dtype, workspace, workspace_bytes,
+                       reinterpret_cast<cudaStream_t>(stream_v));
+}
+
+int64_t fcr_launch_count(void) { return (int64_t)g_launches.load(std::memory_order_relaxed); }
+
+int fcr_poll_device_status(int32_t* code_out) {
+  const DeviceInfo* dev = nullptr;
+  const int rc = device_info(&dev, false);
+  if (rc != FCR_OK) return rc;
+  return check_mailbox(*dev, code_out);
+}
+
+int fcr_self_test_hooks(int64_t wait_limit_cycles, int32_t skip_ring_load) {
+  if (wait_limit_cycles < 0) return fail(FCR_ERR_BAD_ARG, "wait_limit_cycles must not be negative");
+  g_wait_limit_override = wait_limit_cycles;
+  g_skip_ring_load = skip_ring_load < 0 ? -1 : skip_ring_load;
   return FCR_OK;
 }
 
@@ -1455,58 +1520,34 @@ int fcr_finalize(const float* acc, void* out, int32_t out_dtype, int32_t B, int3
   fill_mean(pp, reduction, is_causal, M, N);
   const size_t total = (size_t)pp.BH * N;
   const int blocks = (int)std::min<size_t>((total + 255) / 256, 4096);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
   finalize_kernel<<<blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream_v)>>>(acc, pp);
   const cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "finalize launch");
   return FCR_OK;
 }
 
-int fcr_read_device_status(const void* workspace, void* stream_v, int32_t* code_out) {
-  if (!workspace) return fail(FCR_ERR_BAD_ARG, "null workspace");
-  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
+// Synchronises `stream`, then reads the four leading status words at `status_dev`.
+static int read_status_words(const void* status_dev, cudaStream_t stream, int32_t* code_out) {
   int32_t words[4] = {0, 0, 0, 0};
-  cudaError_t e = cudaMemcpyAsync(words, workspace, sizeof(words), cudaMemcpyDeviceToHost, stream);
+  cudaError_t e = cudaMemcpyAsync(words, status_dev, sizeof(words), cudaMemcpyDeviceToHost, stream);
   if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpyAsync(status)");
   e = cudaStreamSynchronize(stream);
   if (e != cudaSuccess) return cuda_fail(e, "cudaStreamSynchronize");
   if (code_out) *code_out = words[0];
-  if (words[0] != ST_OK)
-    return fail(FCR_ERR_DEVICE_TIMEOUT,
-                "device status " + std::to_string(words[0]) + " (block " + std::to_string(words[1]) +
-                    ", thread " + std::to_string(words[2]) + ", detail " + std::to_string(words[3]) +
-                    "): a bounded wait inside the kernel expired");
-  return FCR_OK;
+  if (words[0] == ST_OK) return FCR_OK;
+  // the same failure also sits in the device's mailbox: it is reported here, once
+  const DeviceInfo* dev = nullptr;
+  if (device_info(&dev, false) == FCR_OK && dev->mailbox_host) {
+    volatile int* w = dev->mailbox_host;
+    if (w[0] == words[0] && w[1] == words[1] && w[2] == words[2]) w[0] = 0;
+  }
+  return fail(FCR_ERR_DEVICE_TIMEOUT, status_text(words));
 }
 
-int fcr_debug_scores(const fcr_problem* problem, const void* q, const void* k, float* scores,
-                     void* workspace, size_t workspace_bytes, void* stream_v) {
-  if (!problem || !q || !k || !scores) return fail(FCR_ERR_BAD_ARG, "null argument");
-  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
-  fcr_problem pr = *problem;
-  pr.is_causal = 0;
-  fcr_plan pl;
-  int rc = fcr_plan_problem(&pr, 0, &pl);
-  if (rc != FCR_OK) return rc;
-  rc = check_workspace(pl, workspace, workspace_bytes);
-  if (rc != FCR_OK) return rc;
-  uint8_t* ws = reinterpret_cast<uint8_t*>(workspace);
-  CUtensorMap map_q, map_k;
-  rc = make_tensor_map(&map_q, q, pr.in_dtype, pr.D, pr.M, pr.H, pr.B, pr.q_strides);
-  if (rc != FCR_OK) return rc;
-  rc = make_tensor_map(&map_k, k, pr.in_dtype, pr.D, pr.N, pr.H, pr.B, pr.k_strides);
-  if (rc != FCR_OK) return rc;
-  cudaError_t e = cudaMemsetAsync(ws + pl.off_status, 0, kStatusWords * 4, stream);
-  if (e != cudaSuccess) return cuda_fail(e, "cudaMemsetAsync");
-  PassParams pp;
-  fill_common(pp, pr, pl, ws, false);
-  pp.n_split = 1;
-  pp.n_items = pp.BH * pl.row_blocks;
-  pp.dump = scores;
-  int sms = 0;
-  rc = device_sm_count(&sms);
-  if (rc != FCR_OK) return rc;
-  const int ctas = std::min(pp.n_items, sms);
-  return launch_pass_d<PH_DUMP, RED_SUM>(pl.d_pad, false, map_q, map_k, pp, ctas, stream);
+int fcr_read_device_status(const void* workspace, void* stream_v, int32_t* code_out) {
+  if (!workspace) return fail(FCR_ERR_BAD_ARG, "null workspace");
+  return read_status_words(workspace, reinterpret_cast<cudaStream_t>(stream_v), code_out);
 }
 
 // ----------------------------------------------------------------------
@@ -1529,15 +1570,11 @@ static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBy
 static std::mutex g_scratch_mutex;
 static void* g_scratch_addr[64] = {};
 
-static int static_scratch_address(void** out) {
-  int dev = 0;
-  cudaError_t e = cudaGetDevice(&dev);
-  if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
-  if (dev < 0 || dev >= 64) return fail(FCR_ERR_UNSUPPORTED, "device ordinal beyond 63");
+static int static_scratch_address(int dev, void** out) {
   std::lock_guard<std::mutex> lock(g_scratch_mutex);
   if (!g_scratch_addr[dev]) {
     void* ptr = nullptr;
-    e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+    const cudaError_t e = cudaGetSymbolAddress(&ptr, g_static_scratch);
     if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(static scratch)");
     if (!ptr) return fail(FCR_ERR_CUDA, "cudaGetSymbolAddress returned a null address");
     g_scratch_addr[dev] = ptr;
@@ -1549,22 +1586,42 @@ static int static_scratch_address(void** out) {
 int fcr_colreduce_static(const fcr_problem* problem, const void* q, const void* k, void* out,
                          int32_t out_dtype, void* stream_v) {
   if (!problem || !q || !k || !out) return fail(FCR_ERR_BAD_ARG, "null argument");
-  fcr_plan pl;
-  int rc = fcr_plan_problem(problem, 0, &pl);
+  if (out_dtype != FCR_F16 && out_dtype != FCR_BF16 && out_dtype != FCR_F32)
+    return fail(FCR_ERR_BAD_ARG, "invalid out_dtype");
+  // No mailbox is created here (that would be an allocation); one that fcr_colreduce created
+  // earlier on this device is used and checked like there.
+  const DeviceInfo* dev = nullptr;
+  int rc = device_info(&dev, false);
   if (rc != FCR_OK) return rc;
-  if ((size_t)min_workspace_bytes(pl) > kStaticScratchBytes)
+  rc = check_mailbox(*dev, nullptr);
+  if (rc != FCR_OK) return rc;
+  const fcr_plan* pl = nullptr;
+  rc = plan_for_call(*problem, *dev, &pl);
+  if (rc != FCR_OK) return rc;
+  if ((size_t)min_workspace_bytes(*pl) > kStaticScratchBytes)
     return fail(FCR_ERR_WORKSPACE,
-                "this problem needs " + std::to_string(min_workspace_bytes(pl)) +
+                "this problem needs " + std::to_string(min_workspace_bytes(*pl)) +
                     " bytes of scratch but the built-in scratch holds " +
                     std::to_string(kStaticScratchBytes) +
                     " (FCR_STATIC_SCRATCH_BYTES); use fcr_colreduce with a caller-owned workspace");
   void* scratch = nullptr;
-  rc = static_scratch_address(&scratch);
+  rc = static_scratch_address(dev->index, &scratch);
   if (rc != FCR_OK) return rc;
   // Same kernels as fcr_colreduce, handed the built-in array.  The status words
   // and scheduler counters at its start are cleared on the stream by that call;
   // everything else in the array is written before it is read.
-  return fcr_colreduce(problem, q, k, out, out_dtype, scratch, kStaticScratchBytes, stream_v);
+  return run_colreduce(*problem, *pl, *dev, q, k, out, out_dtype, scratch, kStaticScratchBytes,
+                       reinterpret_cast<cudaStream_t>(stream_v));
+}
+
+int fcr_read_device_status_static(void* stream_v, int32_t* code_out) {
+  const DeviceInfo* dev = nullptr;
+  int rc = device_info(&dev, false);
+  if (rc != FCR_OK) return rc;
+  void* scratch = nullptr;
+  rc = static_scratch_address(dev->index, &scratch);
+  if (rc != FCR_OK) return rc;
+  return read_status_words(scratch, reinterpret_cast<cudaStream_t>(stream_v), code_out);
 }
 
 int fcr_topk(const void* scores, int32_t dtype, int32_t rows, int32_t n, int32_t k, void* indices,
@@ -1596,33 +1653,6 @@ int fcr_select_above(const void* scores, int32_t dtype, int32_t rows, int32_t n,
     case FCR_F32: return launch_select<float>(scores, rows, n, threshold, indices, index_bits, counts, stream);
     default: return fail(FCR_ERR_BAD_ARG, "invalid dtype");
   }
-}
-
-double fcr_probe_ex2_rate(int32_t repeats) {
-  int sms = 0;
-  if (device_sm_count(&sms) != FCR_OK) return 0.0;
-  float* sink = nullptr;
-  if (cudaMalloc(&sink, 256) != cudaSuccess) return 0.0;
-  const int iters = 4096, threads = 1024, blocks = sms * 2;
-  cudaEvent_t a, b;
-  cudaEventCreate(&a);
-  cudaEventCreate(&b);
-  ex2_probe_kernel<<<blocks, threads>>>(sink, iters);
-  double best = 0.0;
-  for (int r = 0; r < std::max(repeats, 1); ++r) {
-    cudaEventRecord(a);
-    ex2_probe_kernel<<<blocks, threads>>>(sink, iters);
-    cudaEventRecord(b);
-    if (cudaEventSynchronize(b) != cudaSuccess) break;
-    float ms = 0.f;
-    cudaEventElapsedTime(&ms, a, b);
-    const double rate = (double)blocks * threads * 8.0 * iters / (ms * 1e-3);
-    best = std::max(best, rate);
-  }
-  cudaEventDestroy(a);
-  cudaEventDestroy(b);
-  cudaFree(sink);
-  return best;
 }
 
 }  // extern "C"

@@ -66,7 +66,7 @@ keystream_kernel(const __grid_constant__ CUtensorMap tmap_q,
   extern __shared__ __align__(1024) uint8_t smem[];
   const uint32_t base = ptx::smem_u32(smem);
   if ((base & 1023u) != 0) {
-    if (threadIdx.x == 0) report_status(p.status, ST_SMEM_MISALIGNED, (int)base);
+    if (threadIdx.x == 0) report_status(p, ST_SMEM_MISALIGNED, (int)base);
     return;
   }
   const uint32_t s_q = base + L::off_q;
@@ -123,7 +123,6 @@ keystream_kernel(const __grid_constant__ CUtensorMap tmap_q,
 
   if (warp == kKsProducerWarp) {
     // ------------------------------------------------------------ TMA warp
-    PROF_DECL();
     uint32_t ring_seq = 0, q_seq = 0;
     int cur_bh = -1;
     bool ok = true;
@@ -163,7 +162,6 @@ keystream_kernel(const __grid_constant__ CUtensorMap tmap_q,
     }
   } else if (warp == kKsMmaWarp) {
     // ------------------------------------------------------------- MMA warp
-    PROF_DECL();
     uint32_t ring_seq = 0, q_seq = 0;
     uint32_t tm_par = 0;  // bit b: parity of the next use of accumulator buffer b
     int cur_bh = -1;
@@ -231,7 +229,6 @@ keystream_kernel(const __grid_constant__ CUtensorMap tmap_q,
     // -------------------------------------------------------- softmax warps
     // Warpgroup wg folds the tiles that land in accumulator buffer wg: tile t of an item goes
     // to buffer (t - t_lo) mod 4, a property of the item.
-    PROF_DECL();
     const int wg = warp >> 2;
     const int tid_wg = (warp & 3) * 32 + lane;
     const uint32_t lane_field = (uint32_t)((warp & 3) * 32) << 16;

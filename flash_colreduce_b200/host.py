@@ -15,7 +15,7 @@ import torch
 
 from .op import flash_colreduce
 
-__all__ = ["flash_colreduce_host"]
+__all__ = ["flash_colreduce_host", "release_host_buffers"]
 
 
 def flash_colreduce_host(
@@ -61,12 +61,12 @@ def flash_colreduce_host(
     groups = [(bi, h0, min(h0 + group_heads, h)) for bi in range(b) for h0 in range(0, h, group_heads)]
     with torch.cuda.device(device):
         compute = torch.cuda.current_stream(device)
-        copier = torch.cuda.Stream(device)
-        gh = min(group_heads, h)
-        bufs = [(torch.empty((1, gh, m, d), dtype=query.dtype, device=device),
-                 torch.empty((1, gh, n, d), dtype=key.dtype, device=device)) for _ in range(2)]
-        loaded = [torch.cuda.Event() for _ in range(2)]
-        consumed = [torch.cuda.Event() for _ in range(2)]
+        ctx = _context(device, min(group_heads, h), m, n, d, query.dtype)
+        copier, bufs, loaded, consumed = ctx.copier, ctx.bufs, ctx.loaded, ctx.consumed
+        # The staging buffers may still be read by kernels of an earlier call on the compute
+        # stream (or, freshly allocated, by whatever last used their memory): the copy stream
+        # starts behind everything queued on the compute stream so far.
+        copier.wait_stream(compute)
 
         def load(idx):
             bi, h0, h1 = groups[idx]
@@ -90,3 +90,34 @@ def flash_colreduce_host(
             out[bi, h0:h1].copy_(res[0], non_blocking=True)
         compute.synchronize()
     return out
+
+
+class _HostContext:
+    """Copy stream, two pairs of device staging buffers and their events, kept between calls."""
+
+    def __init__(self, device, gh, m, n, d, dtype):
+        self.copier = torch.cuda.Stream(device)
+        self.bufs = [(torch.empty((1, gh, m, d), dtype=dtype, device=device),
+                      torch.empty((1, gh, n, d), dtype=dtype, device=device)) for _ in range(2)]
+        self.loaded = [torch.cuda.Event() for _ in range(2)]
+        self.consumed = [torch.cuda.Event() for _ in range(2)]
+
+
+_CONTEXTS: dict = {}
+
+
+def _context(device, gh, m, n, d, dtype) -> _HostContext:
+    """The staging context for a call signature.  One is kept per device (the last signature
+    used): repeated calls of one shape, the streaming use this function is for, create no
+    stream, buffer or event after the first."""
+    sig = (gh, m, n, d, dtype)
+    hit = _CONTEXTS.get(device)
+    if hit is None or hit[0] != sig:
+        _CONTEXTS.pop(device, None)  # release the old buffers before the new ones are allocated
+        hit = _CONTEXTS[device] = (sig, _HostContext(device, gh, m, n, d, dtype))
+    return hit[1]
+
+
+def release_host_buffers() -> None:
+    """Frees the device staging buffers ``flash_colreduce_host`` keeps between calls."""
+    _CONTEXTS.clear()

@@ -162,6 +162,16 @@ size_t fcr_workspace_bytes(const fcr_problem* problem, int32_t num_sms);
  *
  * Replaces `_flash_colreduce` (flash_colreduce/flash.py:277-308) together
  * with the tail of `flash_colreduce` (flash.py:377-385).
+ *
+ * Every wait inside the kernels is bounded (about one second).  A kernel whose
+ * wait expires gives up, leaves `out` unspecified and records a status code in
+ * the workspace and in a per-device mailbox in mapped host memory; the NEXT
+ * call of fcr_colreduce / fcr_colreduce_static on that device (or
+ * fcr_poll_device_status at any time) then returns FCR_ERR_DEVICE_TIMEOUT
+ * without launching, once, and clears the mailbox.  No synchronisation is
+ * involved.  The first call on a device allocates the mailbox (64 bytes of
+ * pinned host memory, the library's only allocation) and opts the kernels in
+ * to their shared-memory size: make it before any stream capture begins.
  */
 int fcr_colreduce(const fcr_problem* problem, const void* q, const void* k, void* out,
                   int32_t out_dtype, void* workspace, size_t workspace_bytes, void* stream);
@@ -182,8 +192,13 @@ int fcr_colreduce(const fcr_problem* problem, const void* q, const void* k, void
  *
  * - q, k, out, out_dtype, stream: exactly as for fcr_colreduce; the caller
  *   still owns inputs and output.
- * - A problem whose fcr_workspace_bytes() exceeds FCR_STATIC_SCRATCH_BYTES is
- *   rejected with FCR_ERR_WORKSPACE and a message naming both numbers.
+ * - A problem whose required scratch exceeds FCR_STATIC_SCRATCH_BYTES is
+ *   rejected with FCR_ERR_WORKSPACE and a message naming both numbers.  The
+ *   required scratch is fcr_workspace_bytes() for every problem but the decode
+ *   shapes with a score cache (fcr_plan.score_cache): the cache is optional
+ *   here as it is for fcr_colreduce, so for those the limit applies to
+ *   fcr_plan.off_scores, and the cache is used when all of
+ *   fcr_plan.workspace_bytes fits the array.
  * - The first call on each device looks up the array's device address (with
  *   that device current) and caches it; make that first call before any
  *   stream capture begins.
@@ -194,6 +209,9 @@ int fcr_colreduce(const fcr_problem* problem, const void* q, const void* k, void
  *   different streams) race on the array and must be serialised by the caller.
  * - Performs no cudaMalloc / cudaFree and uses no allocating library routine
  *   (tracing, if enabled with fcr_trace_enable, creates CUDA events: leave it off).
+ *   It does not create the status mailbox either; it uses the one an earlier
+ *   fcr_colreduce call on the device created, if any.  Without a mailbox an
+ *   expired device-side wait is visible through fcr_read_device_status_static.
  */
 #define FCR_STATIC_SCRATCH_BYTES (8u << 20)
 int fcr_colreduce_static(const fcr_problem* problem, const void* q, const void* k, void* out,
@@ -217,6 +235,36 @@ int fcr_finalize(const float* acc, void* out, int32_t out_dtype, int32_t B, int3
  */
 int fcr_read_device_status(const void* workspace, void* stream, int32_t* code_out);
 
+/* The same for the built-in scratch array that fcr_colreduce_static uses on the current device. */
+int fcr_read_device_status_static(void* stream, int32_t* code_out);
+
+/*
+ * Looks at the current device's status mailbox without synchronising anything:
+ * FCR_OK when no kernel of an earlier call reported an expired wait, else
+ * FCR_ERR_DEVICE_TIMEOUT (details in fcr_last_error(), raw code in `code_out`,
+ * which may be NULL); the mailbox is cleared, so a failure is reported once.
+ * A failure of a kernel that is still running or queued is seen only after it
+ * has happened: poll after the work is known to be done, or rely on the check
+ * the next fcr_colreduce call makes.
+ */
+int fcr_poll_device_status(int32_t* code_out);
+
+/* Number of kernels this library has launched in the process so far (all threads). */
+int64_t fcr_launch_count(void);
+
+/*
+ * Self-test of the bounded waits, for the calling thread's later
+ * fcr_colreduce calls: `wait_limit_cycles` > 0 replaces the one-second bound
+ * of every device-side wait (in SM clock cycles), and `skip_ring_load` >= 0
+ * makes the first CTA of each pass kernel leave out its skip_ring_load-th
+ * streamed-tile load, so that the waits on that tile expire: the kernels then
+ * give up in an orderly way (no trap, no fault; tensor memory is released) and
+ * the call's failure is reported as described at fcr_colreduce.  (0, -1)
+ * restores normal operation.  The decode (key-streaming) kernels ignore
+ * skip_ring_load.
+ */
+int fcr_self_test_hooks(int64_t wait_limit_cycles, int32_t skip_ring_load);
+
 /*
  * Tracing (the reference has none; its benchmark times whole calls on the
  * host, benchmarks/run.py:59-83).  While enabled for the calling thread, each
@@ -229,15 +277,6 @@ int fcr_read_device_status(const void* workspace, void* stream, int32_t* code_ou
 int fcr_trace_enable(int32_t on);
 int32_t fcr_trace_count(void);
 int fcr_trace_read(int32_t index, float* rows_ms, float* cols_ms);
-
-/*
- * Bring-up diagnostic: writes the raw fp32 scores Q.K^T (no scale, no mask)
- * of every head into `scores`, a (B*H, m_pad, n_pad) fp32 device array, using
- * the same TMA / tcgen05 / tensor-memory pipeline as the operator.  Meant for
- * small problems only.
- */
-int fcr_debug_scores(const fcr_problem* problem, const void* q, const void* k, float* scores,
-                     void* workspace, size_t workspace_bytes, void* stream);
 
 /*
  * Row-wise top-k over a contiguous (rows, n) score array of dtype `dtype`
@@ -264,13 +303,6 @@ int fcr_topk(const void* scores, int32_t dtype, int32_t rows, int32_t n, int32_t
  */
 int fcr_select_above(const void* scores, int32_t dtype, int32_t rows, int32_t n, float threshold,
                      void* indices, int32_t index_bits, int32_t* counts, void* stream);
-
-/*
- * Measurement helper: runs a register-only ex2.approx.ftz.f32 loop on every
- * SM and returns the sustained rate in exponentials per second (the MUFU
- * bound of the roofline).  Synchronises the device.  Returns 0 on error.
- */
-double fcr_probe_ex2_rate(int32_t repeats);
 
 #ifdef __cplusplus
 }

@@ -133,8 +133,23 @@ def test_null_arguments_are_rejected_before_any_device_work():
     assert nat.lib.fcr_plan_problem(None, 148, None) == nat.FCR_ERR_BAD_ARG
     assert nat.lib.fcr_finalize(None, None, 0, 1, 1, 1, 1, 0, 0, None) == nat.FCR_ERR_BAD_ARG
     assert nat.lib.fcr_read_device_status(None, None, None) == nat.FCR_ERR_BAD_ARG
+    assert nat.lib.fcr_self_test_hooks(-1, 0) == nat.FCR_ERR_BAD_ARG
+    assert nat.lib.fcr_self_test_hooks(0, -1) == nat.FCR_OK
     with pytest.raises(RuntimeError, match="status 1"):
         nat.check(nat.FCR_ERR_BAD_ARG, "demo")
+
+
+def test_launch_counter_starts_at_zero_without_a_gpu():
+    import torch
+
+    if not torch.cuda.is_available():
+        assert nat.lib.fcr_launch_count() == 0
+
+
+def test_the_probe_library_exports_its_one_symbol():
+    from flash_colreduce_b200.build import PROBE_PATH
+
+    assert C.CDLL(PROBE_PATH).fcr_probe_ex2_rate is not None
 
 
 def test_plan_item_bounds():

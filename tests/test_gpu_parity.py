@@ -37,8 +37,13 @@ def _rand(shape, seed, dtype=torch.float16):
 def test_native_library_is_loaded():
     from flash_colreduce_b200 import _native as nat
 
+    from flash_colreduce_b200.ex2_probe import ex2_rate
+
     assert nat.lib.fcr_version().decode() == "0.1.0"
-    assert nat.lib.fcr_probe_ex2_rate(1) > 1e12
+    before = nat.lib.fcr_launch_count()
+    _f32(_rand((1, 1, 64, 64), 1).to(_dev()), _rand((1, 1, 64, 64), 2).to(_dev()), "sum", False)
+    assert nat.lib.fcr_launch_count() - before >= 2  # the two pass kernels at least
+    assert ex2_rate(1) > 1e12
 
 
 def test_golden_vectors_fp32(golden):

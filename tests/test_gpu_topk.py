@@ -89,3 +89,54 @@ def test_threshold_selection(dtype, rows, n):
             want = (s[r].float() > thr).nonzero().flatten()
             assert cnt[r].item() == want.numel()
             assert torch.equal(idx[r, : want.numel()], want)
+
+
+@pytest.mark.parametrize("rows_shape,n,k", [((2, 300), 576, 144), ((1, 1000), 2048, 2048)])
+def test_many_short_rows_on_a_side_stream_right_after_the_operator(rows_shape, n, k):
+    """The 256-thread launch shape (at least two rows per SM) must run on the caller's stream: the
+    scores are produced on a non-blocking side stream immediately before the selection reads them."""
+    from flash_colreduce_b200 import flash_colreduce, topk_columns
+
+    dev = _dev()
+    b, h = rows_shape
+    g = torch.Generator().manual_seed(n + k)
+    q = torch.randn(b, h, 96, 64, generator=g).half().to(dev)
+    key = torch.randn(b, h, n, 64, generator=g).half().to(dev)
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream(dev)
+    with torch.cuda.stream(side):
+        for _ in range(3):  # a few calls in a row keep the stream busy ahead of the selection
+            scores = flash_colreduce(q, key, "sum", is_causal=True)
+        vals, idx = topk_columns(scores, k)
+    side.synchronize()
+    scores_cpu, vals, idx = scores.cpu(), vals.cpu(), idx.cpu()
+    assert torch.equal(vals, torch.gather(scores_cpu, -1, idx))
+    want_vals, _ = torch.topk(scores_cpu.float(), k, dim=-1)
+    assert torch.equal(vals.float().sort(dim=-1, descending=True)[0], want_vals)
+
+
+def test_many_short_rows_inside_a_cuda_graph():
+    """Graph capture records only launches made on the capturing stream: rows >= 2 x SMs takes the
+    256-thread launch shape, which has to be captured with the operator that feeds it."""
+    from flash_colreduce_b200 import flash_colreduce, topk_columns
+
+    dev = _dev()
+    g = torch.Generator().manual_seed(11)
+    q = torch.randn(2, 200, 64, 64, generator=g).half().to(dev)
+    key = torch.randn(2, 200, 576, 64, generator=g).half().to(dev)
+    flash_colreduce(q, key, "sum")  # first call outside the capture (one-time attribute set-up)
+    topk_columns(flash_colreduce(q, key, "sum"), 144)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        scores = flash_colreduce(q, key, "sum")
+        vals, idx = topk_columns(scores, 144)
+    q.copy_(torch.randn(q.shape, generator=g).half())  # new inputs: the replay must see them
+    graph.replay()
+    torch.cuda.synchronize()
+    scores_cpu = scores.cpu()
+    assert torch.equal(vals.cpu(), torch.gather(scores_cpu, -1, idx.cpu()))
+    want_vals, _ = torch.topk(scores_cpu.float(), 144, dim=-1)
+    assert torch.equal(vals.cpu().float().sort(dim=-1, descending=True)[0], want_vals)
+    fresh = flash_colreduce(q, key, "sum")
+    assert torch.equal(fresh.cpu(), scores_cpu)
