@@ -50,11 +50,10 @@ namespace fcr {
 
 enum { PH_ROWS = 1, PH_COLS = 2 };
 
-#ifndef FCR_COLSPLIT
-#define FCR_COLSPLIT 2
-#endif
-constexpr int kColSplit = FCR_COLSPLIT;       // softmax warpgroups sharing one accumulator tile
-constexpr int kSoftmaxWarps = 4 * kSubTiles * kColSplit;
+// Two softmax warpgroups per stationary sub-tile; they fold whole accumulator tiles in turn
+// (warpgroup p folds the tiles that land in accumulator buffer p), independent of each other.
+constexpr int kFoldGroups = 2;
+constexpr int kSoftmaxWarps = 4 * kSubTiles * kFoldGroups;
 constexpr int kProducerWarp = kSoftmaxWarps;
 constexpr int kMmaWarp = kSoftmaxWarps + 1;   // issues the MMAs of sub-tile 0, owns the TMEM allocation
 #ifndef FCR_MMA_PER_BUFFER
@@ -65,15 +64,7 @@ constexpr bool kMmaPerBuffer = FCR_MMA_PER_BUFFER != 0;
 constexpr int kMmaWarps = kMmaPerBuffer ? 2 * kSubTiles : kSubTiles;
 constexpr int kThreads = (kSoftmaxWarps + 1 + kMmaWarps) * 32;
 constexpr int kTmemCols = 512;
-#ifndef FCR_TILE_OWNER
-#define FCR_TILE_OWNER 1
-#endif
-// How the kColSplit softmax warpgroups of a stationary sub-tile share its accumulator tiles:
-// true: they take whole tiles in turn (warpgroup p folds the tiles in buffer p), which keeps
-// them independent of each other; false: every tile is split by column ranges.
-constexpr bool kTileOwner = FCR_TILE_OWNER != 0;
-static_assert(!kTileOwner || kColSplit == 2, "tile ownership alternates between two warpgroups");
-constexpr int kSpan = kTileOwner ? kTile : kTile / kColSplit;  // columns of a tile one thread folds
+constexpr int kSpan = kTile;  // columns of an accumulator tile one thread folds: all of them
 #ifndef FCR_CHUNK_ROWS
 #define FCR_CHUNK_ROWS 64
 #endif
@@ -101,6 +92,7 @@ enum {
   ST_WAIT_TMEM_FULL = 31,
   ST_WAIT_RING_FULL_SM = 32,
   ST_WAIT_LSE_EMPTY = 14,
+  ST_WAIT_LSE_FULL = 27,
   ST_WAIT_SCHED_EMPTY = 13,
   ST_WAIT_SCHED_FULL = 26,
   ST_WAIT_SCHED_FULL_SM = 38,
@@ -177,7 +169,7 @@ struct SmemLayout {
   static constexpr int off_ring = off_stat + KS * kSubTiles * kTileBytes;
   static constexpr int off_lse = off_ring + KR * kSlotBytes;
   static constexpr int off_merge = off_lse + KL * kLseBytes;  // float2 [2 slots][kSubTiles][kTile]
-  static constexpr int kMergeBytes = (kColSplit > 1) ? 2 * kSubTiles * kTile * 8 : 0;
+  static constexpr int kMergeBytes = 2 * kSubTiles * kTile * 8;
   static constexpr int off_bars = off_merge + kMergeBytes;
   static constexpr int KI = 4;                   // work items announced ahead of their consumers
   static constexpr int kNumBars = 2 * KS + 2 * KR + 8 + 8 + 2 * KI + 2 * KL;
@@ -304,13 +296,13 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
     }
     if (lane < KL) {
       ptx::mbar_init(bar_lse_full(lane), 1);
-      ptx::mbar_init(bar_lse_empty(lane), kSoftmaxWarps);
+      ptx::mbar_init(bar_lse_empty(lane), 4 * kSubTiles);
     }
     if (lane < 4) {
       const uint32_t a = (uint32_t)lane >> 1, ts = (uint32_t)lane & 1u;
       ptx::mbar_init(bar_tm_full(a, ts), 1);
-      ptx::mbar_init(bar_tm_empty(a, ts), kTileOwner ? 4 : 4 * kColSplit);
-      ptx::mbar_init(bar_merge_full(a, ts), kColSplit > 1 ? 4 * (kColSplit - 1) : 1);
+      ptx::mbar_init(bar_tm_empty(a, ts), 4);
+      ptx::mbar_init(bar_merge_full(a, ts), 4);
       ptx::mbar_init(bar_merge_empty(a, ts), 4);
     }
     if (lane < KI) {
@@ -463,7 +455,7 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
     // Accumulator buffer of a tile = (its index within the work item + the item's parity) mod 2,
     // so that the warpgroup that folds it does not depend on which items this CTA happened to get;
     // tm_use[b] counts the uses of buffer b and gives its barrier phase.
-    uint32_t ring_seq = 0, item_seq = 0;
+    uint32_t ring_seq = 0, item_seq = 0, tile_seq = 0;
     uint32_t tm_use[2] = {0, 0};
     bool ok = true;
     for (;; ++item_seq) {
@@ -479,10 +471,26 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
       if (!ok) break;
       ptx::tc_fence_after_sync();
       const uint32_t a_addr = s_stat + (ks * kSubTiles + a) * L::kTileBytes;
-      for (int t = g.c_lo; ok && t < g.c_hi; ++t) {
+      for (int t = g.c_lo; ok && t < g.c_hi; ++t, ++tile_seq) {
         const uint32_t ts = (uint32_t)(t - g.t_lo[a] + g.par) & 1u;
-        const bool my_tile =
-            t >= g.t_lo[a] && t < g.t_hi[a] && (!kMmaPerBuffer || (int)ts == my_buf);
+        const bool in_range = t >= g.t_lo[a] && t < g.t_hi[a];
+        const bool my_tile = in_range && (!kMmaPerBuffer || (int)ts == my_buf);
+        if (PHASE == PH_COLS) {
+          // The softmax warps read a tile's lse values from the lse ring once its product is in
+          // tensor memory, without waiting on the lse barrier themselves: this warp waits for the
+          // values before it issues the tile's MMAs, so a completed product implies they have
+          // landed.  An lse slot is released by eight arrivals, four per sub-tile: the four warps
+          // that fold the tile for the sub-tile, or, when the tile is outside the sub-tile's range,
+          // this warp on their behalf -- after its own wait, so that the arrivals of a use of the
+          // slot can never reach the barrier before the use before it has completed.
+          const uint32_t sl = tile_seq % KL, lph = (tile_seq / KL) & 1u;
+          ok = WAIT(bar_lse_full(sl), lph, ST_WAIT_LSE_FULL);
+          if (!ok) break;
+          if (!in_range && my_buf == 0) {
+            if (lane == 0) ptx::mbar_arrive_count(bar_lse_empty(sl), 4);
+            __syncwarp();
+          }
+        }
         // a streamed tile arrives in kPieces ring slots (one, or two halves of the row width)
 #pragma unroll
         for (int piece = 0; piece < L::kPieces; ++piece, ++ring_seq) {
@@ -547,16 +555,16 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
   } else {
     // -------------------------------------------------------- softmax warps
     // Warp w reads tensor-memory lanes 32*(w%4).. (a hardware rule), belongs to
-    // stationary sub-tile a and folds columns [part*kSpan, (part+1)*kSpan) of
-    // each of that sub-tile's accumulator tiles.
+    // stationary sub-tile a and to fold group `part` of it: it folds the accumulator
+    // tiles of sub-tile a that land in buffer `part`, all 128 columns of each.
     const int a = (warp >> 2) % kSubTiles;
     const int part = warp / (4 * kSubTiles);
     const int tid_wg = (warp & 3) * 32 + lane;
     const uint32_t lane_field = (uint32_t)((warp & 3) * 32) << 16;
-    const int col_base = kTileOwner ? 0 : part * kSpan;  // first accumulator column this thread folds
     float2* merge_buf = reinterpret_cast<float2*>(smem + L::off_merge);
     uint32_t ring_base = 0, merge_seq = 0;
-    uint32_t tm_use[2] = {0, 0};  // uses of each accumulator buffer of sub-tile a seen by this warp
+    uint32_t tm_use = 0;  // uses of accumulator buffer (a, part) so far: gives its barrier phase
+    const uint32_t taddr = tmem_base + lane_field + (uint32_t)(a * 2 + part) * kTile;
     bool ok = true;
     for (uint32_t item_seq = 0;; ++item_seq) {
       const uint32_t si = item_seq % KI, sph = (item_seq / KI) & 1u;
@@ -587,69 +595,50 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
         if (p.causal) mask_from = (int)min((long long)mask_from, ((long long)g.r0[a] + p.off + 1) >> 7);
       }
 
-      uint32_t rs = ring_base;
-      for (int t = g.c_lo; ok && t < g.c_hi; ++t, ++rs) {
-        const bool in_range = (t >= g.t_lo[a]) && (t < g.t_hi[a]);
-        // accumulator buffer of this tile: alternates within the item, starting from the
-        // parity of the item's index (a property of the item, so the result does not depend
-        // on which CTA runs it; short items then spread over both warpgroups)
-        const uint32_t ts = (uint32_t)(t - g.t_lo[a] + g.par) & 1u;
-        // with tile ownership a warpgroup folds every other tile of its sub-tile
-        const bool active = in_range && (!kTileOwner || (int)ts == part);
-        const uint32_t sl = rs % KL, lph = (rs / KL) & 1u;
-        // columns pass: the folding warps read the tile's lse values from the lse ring.  Every
-        // softmax warp waits for every lse slot and releases it, whether or not it folds the
-        // tile: a warp that skipped phases of a barrier could pass a later parity wait on a
-        // stale phase and release the slot before it had been filled.
-        constexpr bool holds_slot = PHASE == PH_COLS;
-        if (holds_slot) {
-          ok = WAIT(bar_lse_full(sl), lph, ST_WAIT_RING_FULL_SM);
-          if (!ok) break;
-        }
-        if (active) {
-          const uint32_t tph = (ts ? tm_use[1] : tm_use[0]) & 1u;
-          if (ts) ++tm_use[1]; else ++tm_use[0];
-          ok = WAIT(bar_tm_full(a, ts), tph, ST_WAIT_TMEM_FULL);
-          if (!ok) break;
-          ptx::tc_fence_after_sync();
-          const uint32_t taddr =
-              tmem_base + lane_field + (uint32_t)(a * 2 + ts) * kTile + (uint32_t)col_base;
-          const int c0 = t * kTile + col_base;  // streamed index of this thread's first column
-          const bool need_mask = t >= mask_from || t < mask_until;
-          const int lim_lo = valid_lo - c0, lim_hi = valid_hi - c0;
-          const float* lse_s =
-              reinterpret_cast<const float*>(smem + L::off_lse + sl * L::kLseBytes) + col_base;
+      // Tile t of the item goes to accumulator buffer (t - t_lo[a] + par) mod 2: it alternates
+      // within the item, starting from the parity of the item's index (a property of the item,
+      // so the summation order does not depend on which CTA runs it, and short items spread
+      // over both fold groups).  This group folds every other tile of the sub-tile's range.
+      for (int t = g.t_lo[a] + ((part - g.par) & 1); t < g.t_hi[a]; t += 2) {
+        const uint32_t tph = tm_use & 1u;
+        ++tm_use;
+        ok = WAIT(bar_tm_full(a, part), tph, ST_WAIT_TMEM_FULL);
+        if (!ok) break;
+        ptx::tc_fence_after_sync();
+        const int c0 = t * kTile;  // streamed index of the tile's first column
+        const bool need_mask = t >= mask_from || t < mask_until;
+        const int lim_lo = valid_lo - c0, lim_hi = valid_hi - c0;
+        // columns pass: the tile's lse values, in the lse ring slot of the tile's running number
+        // (they have landed: the MMA warp waited for them before it issued the tile's MMAs)
+        const uint32_t sl = (ring_base + (uint32_t)(t - g.c_lo)) % KL;
+        const float* lse_s = reinterpret_cast<const float*>(smem + L::off_lse + sl * L::kLseBytes);
 
-          constexpr int kChunk = (PHASE == PH_COLS) ? kChunkCols : kChunkRows;
-          uint32_t ra[kChunk];
-          auto consume = [&](const uint32_t* r, int c) {
-            if constexpr (PHASE == PH_ROWS) {
-              if (need_mask)
-                rows_chunk<true, kChunk>(r, p.scale2, lim_hi - kChunk * c, m_run, l_run);
-              else
-                rows_chunk<false, kChunk>(r, p.scale2, kChunk, m_run, l_run);
-            } else {
-              if (need_mask)
-                cols_chunk<RED, true, kChunk>(r, lse_s + kChunk * c, p.scale2, lim_lo - kChunk * c,
-                                              lim_hi - kChunk * c, acc);
-              else
-                cols_chunk<RED, false, kChunk>(r, lse_s + kChunk * c, p.scale2, 0, kChunk, acc);
-            }
-          };
-          // one chunk at a time: the other warps of the scheduler cover the load latency
+        constexpr int kChunk = (PHASE == PH_COLS) ? kChunkCols : kChunkRows;
+        uint32_t ra[kChunk];
+        // one chunk at a time: the other warps of the scheduler cover the load latency
 #pragma unroll
-          for (int c = 0; c < kSpan / kChunk; ++c) {
-            ptx::tmem_ld<kChunk>(taddr + c * kChunk, ra);
-            ptx::tmem_ld_wait<kChunk>(ra);
-            if (c + 1 == kSpan / kChunk) {
-              ptx::tc_fence_before_sync();
-              __syncwarp();
-              if (lane == 0) ptx::mbar_arrive(bar_tm_empty(a, ts));
-            }
-            consume(ra, c);
+        for (int c = 0; c < kSpan / kChunk; ++c) {
+          ptx::tmem_ld<kChunk>(taddr + c * kChunk, ra);
+          ptx::tmem_ld_wait<kChunk>(ra);
+          if (c + 1 == kSpan / kChunk) {
+            ptx::tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(bar_tm_empty(a, part));
+          }
+          if constexpr (PHASE == PH_ROWS) {
+            if (need_mask)
+              rows_chunk<true, kChunk>(ra, p.scale2, lim_hi - kChunk * c, m_run, l_run);
+            else
+              rows_chunk<false, kChunk>(ra, p.scale2, kChunk, m_run, l_run);
+          } else {
+            if (need_mask)
+              cols_chunk<RED, true, kChunk>(ra, lse_s + kChunk * c, p.scale2, lim_lo - kChunk * c,
+                                            lim_hi - kChunk * c, acc);
+            else
+              cols_chunk<RED, false, kChunk>(ra, lse_s + kChunk * c, p.scale2, 0, kChunk, acc);
           }
         }
-        if (holds_slot) {
+        if (PHASE == PH_COLS) {
           __syncwarp();
           if (lane == 0) ptx::mbar_arrive(bar_lse_empty(sl));
         }
@@ -659,8 +648,8 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
       if (g.r0[a] >= p.LS) continue;  // nothing to write for this sub-tile
 
       // ------------------------------------------------------ item epilogue
-      // The kColSplit threads that share a row / column combine their partial
-      // state through shared memory; the thread of part 0 writes the result.
+      // The two threads that share a row / column (one per fold group) combine their
+      // partial state through shared memory; the thread of group 0 writes the result.
       float v0, v1 = 0.f;
       if (PHASE == PH_ROWS) {
         v0 = m_run;
@@ -670,7 +659,7 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
       } else {
         v0 = fmaxf(fmaxf(acc[0], acc[1]), fmaxf(acc[2], acc[3]));
       }
-      if (kColSplit > 1) {
+      {
         const uint32_t slot = merge_seq & 1u, mph = (merge_seq >> 1) & 1u;
         float2* cell = merge_buf + ((size_t)slot * kSubTiles + a) * kTile + tid_wg;
         ++merge_seq;

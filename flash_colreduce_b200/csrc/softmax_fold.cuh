@@ -16,6 +16,14 @@ enum { RED_SUM = 0, RED_MAX = 1 };
 // Pairs of exponentials, out of every 8 pairs (16 elements), that are evaluated by the
 // polynomial on the FMA pipe instead of MUFU: 2 = a quarter of all exponentials.
 constexpr int kPolyOf8 = FCR_POLY;
+#ifndef FCR_POLY_ROWS
+#define FCR_POLY_ROWS FCR_POLY
+#endif
+#ifndef FCR_POLY_COLS
+#define FCR_POLY_COLS FCR_POLY
+#endif
+constexpr int kPolyRows = FCR_POLY_ROWS;  // the share in the rows pass
+constexpr int kPolyCols = FCR_POLY_COLS;  // the share in the columns pass (sum / mean)
 // Spreads POLY chosen pairs evenly over each group of 8 pairs.
 __host__ __device__ constexpr bool poly_pair(int e, int poly) { return ((((e & 15) >> 1) * poly) & 7) < poly; }
 
@@ -23,7 +31,7 @@ __host__ __device__ constexpr bool poly_pair(int e, int poly) { return ((((e & 1
 // One 32-column chunk of a query row: online max / sum in the base-2 domain
 // (flash_colreduce/flash.py:71-78).  `nvalid` = number of leading columns of
 // the chunk this row may attend (only read when MASKED).
-template <bool MASKED, int W, int POLY = kPolyOf8>
+template <bool MASKED, int W, int POLY = kPolyRows>
 __device__ __forceinline__ void rows_chunk(const uint32_t* r, float scale2, int nvalid,
                                            float& m_run, float& l_run) {
   float x[W];
@@ -76,7 +84,7 @@ __device__ __forceinline__ void rows_chunk(const uint32_t* r, float scale2, int 
 // the column's accumulators (flash_colreduce/flash.py:120-124).  Queries
 // e in [e_lo, e_hi) of the chunk are valid (only read when MASKED).  For max
 // the fold is done on the exponent, exp2 being monotonic.
-template <int RED, bool MASKED, int W, int POLY = kPolyOf8>
+template <int RED, bool MASKED, int W, int POLY = kPolyCols>
 __device__ __forceinline__ void cols_chunk(const uint32_t* r, const float* neg_lse,
                                            float scale2, int e_lo, int e_hi, float (&acc)[4]) {
 #pragma unroll
