@@ -32,9 +32,10 @@ sys.path.insert(0, ROOT)
 WORKLOAD = dict(B=1, H=64, M=131072, N=131072, D=128, causal=True, reduction="sum")
 METRIC = "attn_scores_reduced_per_s"
 UNIT = "scores/s"
-# DRAM bytes (read + write) of one pass-kernel launch per byte of Q and K it is given, measured with ncu
-# (profiles/): re-streaming of the operands is served by the L2, so the traffic is the inputs once.
-TRAFFIC_PER_INPUT_BYTE = 1.028
+# DRAM bytes (read + write) of one pass-kernel launch per byte of Q and K it is given, measured with ncu on a
+# two-head slice of this workload (same 64 MiB heads, same interleaving of two heads; profiles/): the
+# re-streaming of the operands is served by the L2 (98 % hits), part of a head is read from DRAM more than once.
+TRAFFIC_PER_INPUT_BYTE = {"rows": 1.553, "cols": 1.268}
 
 
 def _peaks():
@@ -349,7 +350,7 @@ def run_ours(args):
                 "frac": achieved / peak_sustained,
                 # DRAM bytes of one pass launch per byte of Q and K, from an ncu capture of a two-head slice of
                 # this workload (64 MiB heads, as here); the traffic grows with the heads a rank holds
-                "traffic": int(TRAFFIC_PER_INPUT_BYTE * 2 * heads * (M + N) * D),
+                "traffic": int(TRAFFIC_PER_INPUT_BYTE["rows" if rows_ms >= cols_ms else "cols"] * 2 * heads * (M + N) * D),
                 "algorithmic_flops_per_score_per_launch": 2 * D, "peak_kind": f"{peak_kind} sustained bf16 (kernel timed inside a long step)",
                 "kernel": "pass_kernel (rows pass)" if rows_ms >= cols_ms else "pass_kernel (columns pass)",
                 "rows_pass_ms": rows_ms, "cols_pass_ms": cols_ms,

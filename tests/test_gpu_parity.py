@@ -120,6 +120,29 @@ def test_config_vlm_pruning_heads():
         assert_parity(_f32(q.to(dev), k.to(dev), red, True), oracle_colreduce(q, k, red, True), red)
 
 
+def test_config_vlm_pruning_whole_problem():
+    """The whole B=4, H=32, M=N=8192, d=128 causal configuration: one head of every batch entry
+    against the oracle (mean, the configuration's reduction), every head through properties."""
+    dev = _dev()
+    b, h, n, d = 4, 32, 8192, 128
+    q, k = _vlm_inputs(b, h, n, d, 30)
+    qd, kd = q.to(dev), k.to(dev)
+    mean = _f32(qd, kd, "mean", True)
+    total = _f32(qd, kd, "sum", True)
+    for bi, hi in ((0, 5), (1, 13), (2, 22), (3, 31)):
+        want = oracle_colreduce(q[bi:bi + 1, hi:hi + 1], k[bi:bi + 1, hi:hi + 1], "mean", True)
+        assert_parity(mean[bi:bi + 1, hi:hi + 1], want, "mean")
+    # every softmax row sums to one: the column sums of a head add up to its number of rows
+    torch.testing.assert_close(total.double().sum(dim=-1).cpu(), torch.full((b, h), float(n), dtype=torch.float64),
+                               rtol=1e-4, atol=0)
+    # M == N: column j is seen by the n - j queries j .. n-1, and that is its mean divisor (flash.py:377-384)
+    div = torch.arange(n, 0, -1, dtype=torch.float32, device=dev)
+    torch.testing.assert_close(mean * div, total, rtol=1e-6, atol=1e-30)
+    assert bool((mean > 0).all()) and bool((mean <= 1 + 1e-6).all())
+    # the four sink keys take a visible share of every row's probability mass
+    assert float((total[..., :4].sum(dim=-1) / n).min()) > 0.05
+
+
 def test_long_context_properties():
     """M=N=131072, d=128, causal: checked through size-independent properties and row slices."""
     from flash_colreduce_b200 import colreduce_partial
