@@ -378,7 +378,7 @@ def run_msplit(args):
     """Fewer heads than GPUs: the rows of a head are split over its ranks, one all-reduce combines."""
     from flash_colreduce_b200 import _native as nat
     from flash_colreduce_b200 import colreduce_partial, valid_scores
-    from flash_colreduce_b200.sharding import plan_shards, sharded_colreduce
+    from flash_colreduce_b200.sharding import NativeComm, plan_shards, sharded_colreduce, sharded_colreduce_native
 
     dd = _Dist(args)
     world, rank, dev = dd.world, dd.rank, dd.dev
@@ -390,8 +390,11 @@ def run_msplit(args):
     q, k = _head_inputs(dev, range(spec.head_lo, spec.head_hi), M, N, D)
     scale = D ** -0.5
 
+    # the library's own multi-GPU entry (fcr_colreduce_sharded) on a communicator it made itself
+    comm = NativeComm() if world > 1 else None
+
     def step(reduction="sum"):
-        return sharded_colreduce(q, k, reduction, True, scale, spec=spec, total_heads=H)
+        return sharded_colreduce_native(q, k, reduction, True, scale, total_heads=H, comm=comm, world=world, rank=rank)
 
     warmup = max(args.warmup, 3)
     for _ in range(warmup):
@@ -441,6 +444,9 @@ def run_msplit(args):
     # ---- invariance under the shard count: head 0 computed whole on one GPU against the sharded result
     check = {}
     out_max = step("max")
+    # the Python driver over torch.distributed (same plan, same kernels) must agree with the C entry
+    via_torch = sharded_colreduce(q, k, "max", True, scale, spec=spec, total_heads=H)
+    agree = bool(torch.equal(via_torch, out_max))
     if rank == 0:
         from flash_colreduce_b200 import flash_colreduce
 
@@ -449,6 +455,7 @@ def run_msplit(args):
         whole_max = flash_colreduce(q0, k0_, "max", is_causal=True)
         rel = ((out[0].float() - whole_sum[0, 0].float()).abs() / whole_sum[0, 0].float().abs().clamp_min(1e-6)).max()
         check = {"max_bitwise_equal_to_one_gpu": bool(torch.equal(out_max[0], whole_max[0, 0])),
+                 "max_bitwise_equal_to_torch_distributed_driver": agree,
                  "sum_max_rel_diff_to_one_gpu": float(rel), "column_sums_total": float(out.float().sum().item()),
                  "column_sums_expected": float(H * M)}
     if rank == 0:
@@ -466,6 +473,8 @@ def run_msplit(args):
             "shard_invariance": check, "gpu_launches": launches, "clocks": clocks.summary(),
         }
         print(json.dumps(line), flush=True)
+    if comm is not None:
+        comm.close()
     dd.close()
 
 

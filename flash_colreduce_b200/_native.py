@@ -16,6 +16,8 @@ FCR_ERR_UNSUPPORTED = 2
 FCR_ERR_WORKSPACE = 3
 FCR_ERR_DEVICE_TIMEOUT = 4
 FCR_ERR_CUDA = 5
+FCR_ERR_NCCL = 6
+FCR_NCCL_ID_BYTES = 128
 
 FCR_F16, FCR_BF16, FCR_F32 = 0, 1, 2
 FCR_SUM, FCR_MEAN, FCR_MAX = 0, 1, 2
@@ -40,6 +42,12 @@ EXPORTS = (
     "fcr_poll_device_status",
     "fcr_launch_count",
     "fcr_self_test_hooks",
+    "fcr_plan_shards",
+    "fcr_comm_unique_id",
+    "fcr_comm_init",
+    "fcr_comm_destroy",
+    "fcr_sharded_workspace_bytes",
+    "fcr_colreduce_sharded",
 )
 
 
@@ -76,7 +84,19 @@ class Plan(C.Structure):
         ("off_part_m", C.c_int64), ("off_part_l", C.c_int64), ("off_part_out", C.c_int64),
         ("workspace_bytes", C.c_int64),
         ("key_stream", C.c_int32), ("key_chunks", C.c_int32),
-        ("off_scores", C.c_int64), ("score_cache", C.c_int32), ("reserved", C.c_int32),
+        ("off_scores", C.c_int64), ("score_cache", C.c_int32), ("static_schedule", C.c_int32),
+    ]
+
+
+class Shard(C.Structure):
+    """Mirror of ``fcr_shard``."""
+
+    _fields_ = [
+        ("rank", C.c_int32), ("world", C.c_int32),
+        ("head_lo", C.c_int32), ("head_hi", C.c_int32),
+        ("n_ranges", C.c_int32),
+        ("row_lo", C.c_int32 * 2), ("row_hi", C.c_int32 * 2),
+        ("needs_reduce", C.c_int32),
     ]
 
 
@@ -127,6 +147,20 @@ def _load() -> C.CDLL:
     lib.fcr_launch_count.restype = C.c_int64
     lib.fcr_self_test_hooks.argtypes = [C.c_int64, C.c_int32]
     lib.fcr_self_test_hooks.restype = C.c_int
+    lib.fcr_plan_shards.argtypes = [C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.POINTER(Shard)]
+    lib.fcr_plan_shards.restype = C.c_int
+    lib.fcr_comm_unique_id.argtypes = [C.c_void_p]
+    lib.fcr_comm_unique_id.restype = C.c_int
+    lib.fcr_comm_init.argtypes = [C.c_void_p, C.c_int32, C.c_int32, C.POINTER(C.c_void_p)]
+    lib.fcr_comm_init.restype = C.c_int
+    lib.fcr_comm_destroy.argtypes = [C.c_void_p]
+    lib.fcr_comm_destroy.restype = C.c_int
+    lib.fcr_sharded_workspace_bytes.argtypes = [C.POINTER(Problem), C.POINTER(Shard)]
+    lib.fcr_sharded_workspace_bytes.restype = C.c_size_t
+    lib.fcr_colreduce_sharded.argtypes = [C.POINTER(Problem), C.POINTER(Shard), C.c_int32, C.c_void_p, C.c_void_p,
+                                          C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_size_t, C.c_void_p,
+                                          C.c_void_p]
+    lib.fcr_colreduce_sharded.restype = C.c_int
     return lib
 
 

@@ -119,7 +119,8 @@ struct PassParams : PassGeom {
   int* host_status;       // the device's status mailbox in mapped host memory (null: none)
   long long wait_limit;   // bound of every device-side wait, in clock64 cycles
   int skip_ring_load;     // self-test: CTA 0's TMA warp leaves out this ring load (-1: none)
-  int* sched_counter;  // zero at launch; hands out work items beyond the first gridDim.x
+  int* sched_counter;  // zero at launch; hands out work items beyond the first gridDim.x (null: round-robin)
+  int clear_status;    // 1: this kernel clears status words 0-3 itself (no memset ran before it)
   int key_tiles;       // key-streaming kernels: 128-key tiles per head
   int fold_cols;       // key-streaming columns pass: M rounded up to a 32-query chunk
 };
@@ -328,6 +329,7 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
   // and wait here for the previous kernel's results (the rows pass's lse, the work counters).
   if (threadIdx.x == 0) ptx::grid_launch_dependents();
   ptx::grid_dependency_wait();
+  if (p.clear_status && blockIdx.x == 0 && threadIdx.x < 4) p.status[threadIdx.x] = 0;
 
   if (warp == kProducerWarp) {
     // ------------------------------------------------------------ TMA warp
@@ -360,8 +362,14 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
     // `pending`; it is broadcast only when the next iteration needs it, so the warp never
     // stalls on the atomic's round trip.
     int pending = 0;
+    int dealt = (int)blockIdx.x;  // round-robin dealing: the item this CTA took last
     auto issue_fetch = [&]() {
-      if (lane == 0) pending = (int)gridDim.x + atomicAdd(p.sched_counter, 1);
+      if (p.sched_counter == nullptr) {
+        dealt += (int)gridDim.x;
+        pending = dealt;
+      } else if (lane == 0) {
+        pending = (int)gridDim.x + atomicAdd(p.sched_counter, 1);
+      }
     };
     const int item = (int)blockIdx.x;
     issue_fetch();
@@ -1048,8 +1056,10 @@ static int launch_pass(const CUtensorMap& stat, const CUtensorMap& strm, const P
     if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute");
     opted_in.fetch_or(bit, std::memory_order_release);
   }
-  // the columns pass follows the rows pass (or its combine kernel) in the stream
-  e = launch_kernel(kern, dim3(ctas), dim3(kThreads), smem, stream, PHASE == PH_COLS, stat, strm, pp);
+  // Every pass kernel may begin its set-up while the kernel before it in the stream drains (they all
+  // wait for that kernel's completion before touching global memory): the columns pass follows the rows
+  // pass or its combine kernel, the rows pass the previous call's last kernel.
+  e = launch_kernel(kern, dim3(ctas), dim3(kThreads), smem, stream, true, stat, strm, pp);
   if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "pass kernel launch");
   return FCR_OK;
@@ -1078,7 +1088,7 @@ static int launch_keystream(const CUtensorMap& map_q, const CUtensorMap& map_k, 
     if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute");
     opted_in.fetch_or(bit, std::memory_order_release);
   }
-  e = launch_kernel(kern, dim3(ctas), dim3(kKsThreads), smem, stream, PHASE == PH_COLS, map_q, map_k, pp);
+  e = launch_kernel(kern, dim3(ctas), dim3(kKsThreads), smem, stream, true, map_q, map_k, pp);
   if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "key-streaming kernel launch");
   return FCR_OK;
@@ -1126,7 +1136,8 @@ static void fill_common(PassParams& pp, const fcr_problem& pr, const fcr_plan& p
   pp.part_l = reinterpret_cast<float*>(ws + pl.off_part_l);
   pp.part_out = reinterpret_cast<float*>(ws + pl.off_part_out);
   pp.status = reinterpret_cast<int*>(ws + pl.off_status);
-  pp.sched_counter = pp.status + (cols ? 9 : 8);
+  pp.sched_counter = pl.static_schedule ? nullptr : pp.status + (cols ? 9 : 8);
+  pp.clear_status = (pl.static_schedule && !cols) ? 1 : 0;  // the first kernel of a call that ran no memset
   pp.host_status = host_status;
   pp.wait_limit = g_wait_limit_override > 0 ? g_wait_limit_override : kWaitLimitCycles;
   pp.skip_ring_load = g_skip_ring_load;
@@ -1334,8 +1345,13 @@ static int run_colreduce(const fcr_problem& pr, const fcr_plan& pl, const Device
   rc = make_tensor_map(&map_k, k, pr.in_dtype, pr.D, pr.N, pr.H, pr.B, pr.k_strides);
   if (rc != FCR_OK) return rc;
 
-  cudaError_t e = cudaMemsetAsync(ws + pl.off_status, 0, kStatusWords * 4, stream);
-  if (e != cudaSuccess) return cuda_fail(e, "cudaMemsetAsync");
+  // Plans that draw work items from a counter clear it (and the status words) here; the others
+  // clear their four status words in the first kernel and save this stream operation.
+  cudaError_t e = cudaSuccess;
+  if (!pl.static_schedule) {
+    e = cudaMemsetAsync(ws + pl.off_status, 0, kStatusWords * 4, stream);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaMemsetAsync");
+  }
 
   if (pl.key_stream) {
     // Decode shapes: both passes stream the key tiles past the head's one query tile.
@@ -1645,3 +1661,5 @@ int fcr_select_above(const void* scores, int32_t dtype, int32_t rows, int32_t n,
 }
 
 }  // extern "C"
+
+#include "sharded.cuh"

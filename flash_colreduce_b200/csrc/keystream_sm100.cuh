@@ -114,6 +114,7 @@ keystream_kernel(const __grid_constant__ CUtensorMap tmap_q,
   const uint32_t tmem_base = *tmem_slot;
   if (threadIdx.x == 0) ptx::grid_launch_dependents();
   ptx::grid_dependency_wait();
+  if (p.clear_status && blockIdx.x == 0 && threadIdx.x < 4) p.status[threadIdx.x] = 0;
 
   // CTA c runs the contiguous items [c*I/G, (c+1)*I/G): consecutive items mostly belong to
   // one head, whose query tile is then loaded once.  Every warp derives the sequence itself.

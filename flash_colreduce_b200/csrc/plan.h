@@ -286,6 +286,11 @@ inline int plan_problem(const fcr_problem& p, int num_sms, fcr_plan& pl, std::st
     pl.short_items = 0;
   }
 
+  // Small problems (at most two work items per CTA) deal their items round-robin: no work
+  // counter, so nothing in the workspace needs clearing before the kernels.  The key-streaming
+  // kernels never use the counter.
+  pl.static_schedule = (pl.key_stream || (pl.row_items <= 2 * pl.row_ctas && pl.col_items <= 2 * pl.col_ctas)) ? 1 : 0;
+
   int64_t scores = 0;
   if (!causal) {
     scores = (int64_t)p.M * p.N;

@@ -36,7 +36,8 @@ typedef enum fcr_status {
   FCR_ERR_UNSUPPORTED = 2,    /* shape / dtype / stride the sm_100a kernels cannot take */
   FCR_ERR_WORKSPACE = 3,      /* workspace missing, misaligned or smaller than fcr_workspace_bytes() */
   FCR_ERR_DEVICE_TIMEOUT = 4, /* a bounded device-side wait expired; see fcr_read_device_status */
-  FCR_ERR_CUDA = 5            /* a CUDA runtime / driver call failed */
+  FCR_ERR_CUDA = 5,           /* a CUDA runtime / driver call failed */
+  FCR_ERR_NCCL = 6            /* NCCL could not be loaded or one of its calls failed */
 } fcr_status;
 
 typedef enum fcr_dtype { FCR_F16 = 0, FCR_BF16 = 1, FCR_F32 = 2 } fcr_dtype;
@@ -110,7 +111,9 @@ typedef struct fcr_plan {
                              * workspace and optional: a workspace of only off_scores bytes is accepted, the
                              * columns pass then sweeps K a second time */
   int32_t score_cache;      /* 1 when the columns are reduced from cached scores */
-  int32_t reserved;
+  int32_t static_schedule;  /* 1: work items are dealt round-robin (item, item + CTAs, ...) and nothing in the workspace has
+                             * to be cleared before the kernels (small problems and the key-streaming kernels);
+                             * 0: CTAs draw items from a counter, which one cudaMemsetAsync per call clears */
 } fcr_plan;
 
 /* Library version string, e.g. "0.1.0". */
@@ -226,6 +229,63 @@ int fcr_colreduce_static(const fcr_problem* problem, const void* q, const void* 
  */
 int fcr_finalize(const float* acc, void* out, int32_t out_dtype, int32_t B, int32_t H, int32_t M,
                  int32_t N, int32_t reduction, int32_t is_causal, void* stream);
+
+/*
+ * ---- Several GPUs: one process (rank) per GPU ----------------------------
+ * The reference has no multi-GPU path; these entry points have no counterpart
+ * in it.  Heads are independent, and so are the query rows of a head, so the
+ * work is sharded without any exchange of Q, K or scores: a rank computes
+ * fp32 partial column vectors for its heads / rows, the partials are combined
+ * by ONE all-reduce (sum, or max for FCR_MAX) over NCCL, and the mean divisor
+ * of flash_colreduce/flash.py:377-384 and the cast come last.  NCCL is loaded
+ * at run time (libnccl.so.2, the copy already in the process if there is one).
+ *
+ * fcr_shard says what a rank computes: heads [head_lo, head_hi) of the B*H
+ * heads and, of each of them, the query rows [row_lo[r], row_hi[r]) for
+ * r < n_ranges.  fcr_plan_shards fills it: with heads >= world the heads are
+ * partitioned (one range: all rows; needs_reduce = 0); otherwise world / heads
+ * ranks share a head and rank g of a head takes row chunks g and
+ * 2 * ranks_per_head - 1 - g of 2 * ranks_per_head chunks of whole 128-row
+ * tiles (zig-zag: equal causal work); ranks left over get no heads and only
+ * take part in the all-reduce.
+ */
+typedef struct fcr_shard {
+  int32_t rank, world;
+  int32_t head_lo, head_hi;
+  int32_t n_ranges;
+  int32_t row_lo[2], row_hi[2];
+  int32_t needs_reduce;     /* rows of a head are spread over several ranks */
+} fcr_shard;
+
+int fcr_plan_shards(int32_t heads, int32_t M, int32_t world, int32_t rank, fcr_shard* out);
+
+/*
+ * Communicator: rank 0 obtains FCR_NCCL_ID_BYTES bytes from fcr_comm_unique_id
+ * and hands them to every rank by whatever means the application has; every
+ * rank then calls fcr_comm_init with its own device current.  The handle is an
+ * ncclComm_t; an application that already has one may pass its own instead.
+ */
+#define FCR_NCCL_ID_BYTES 128
+int fcr_comm_unique_id(void* id_out);
+int fcr_comm_init(const void* id, int32_t world, int32_t rank, void** comm_out);
+int fcr_comm_destroy(void* comm);
+
+/*
+ * The sharded operator.  `local` describes the tensors this rank holds: B = 1,
+ * H = head_hi - head_lo heads, ALL M rows and N keys of them (q, k, strides,
+ * dtype as for fcr_colreduce), and the whole problem's reduction, mask and
+ * scale.  acc: device fp32 (total_heads, N), scratch for the partial vectors;
+ * out: device (total_heads, N) of out_dtype, the full result on every rank.
+ * workspace: at least fcr_sharded_workspace_bytes(local, shard), 256-byte
+ * aligned.  comm may be NULL when shard->world == 1.  Everything is queued on
+ * `stream`: a memset of acc, fcr_colreduce's kernels per row range, one small
+ * fold kernel per range, ncclAllReduce, the finalize kernel; no host
+ * synchronisation.
+ */
+size_t fcr_sharded_workspace_bytes(const fcr_problem* local, const fcr_shard* shard);
+int fcr_colreduce_sharded(const fcr_problem* local, const fcr_shard* shard, int32_t total_heads, const void* q,
+                          const void* k, float* acc, void* out, int32_t out_dtype, void* workspace,
+                          size_t workspace_bytes, void* comm, void* stream);
 
 /*
  * Synchronises `stream` and reads the device status words of a workspace

@@ -65,15 +65,17 @@ def test_small_problems_are_split_to_fill_the_gpu():
     pl = nat.plan(_problem(1, 32, 128, 4096, 128, causal=True), 148)
     assert pl.row_blocks == 1 and pl.row_splits > 1
     assert pl.off_part_m > 0 and pl.off_part_l > pl.off_part_m
-    # plenty of blocks: no split, no partial buffers
+    # plenty of blocks: no split, no partial buffers, items drawn from a counter
     pl = nat.plan(_problem(4, 32, 8192, 8192, 128, causal=True), 148)
-    assert pl.row_splits == 1 and pl.col_splits == 1 and pl.off_part_out == 0
+    assert pl.row_splits == 1 and pl.col_splits == 1 and pl.off_part_out == 0 and pl.static_schedule == 0
+    # at most two items per CTA: dealt round-robin, nothing to clear
+    assert nat.plan(_problem(8, 16, 512, 512, 64), 148).static_schedule == 1
 
 
 def test_decode_plans_stream_the_keys():
     # one query tile, 256 key tiles: key streaming; the last fields of the struct line up with the C layout
     pl = nat.plan(_problem(8, 32, 64, 32768, 128, causal=True), 148)
-    assert pl.key_stream == 1 and pl.key_chunks >= 1 and pl.score_cache == 0 and pl.off_scores == 0 and pl.reserved == 0
+    assert pl.key_stream == 1 and pl.key_chunks >= 1 and pl.score_cache == 0 and pl.off_scores == 0 and pl.static_schedule == 1
     assert pl.row_splits == 4 * pl.key_chunks and pl.col_splits == 1
     assert pl.row_items == pl.col_items == 8 * 32 * pl.key_chunks
     # at most 16 queries: the raw scores are cached at the end of the workspace

@@ -23,7 +23,7 @@ def _worker(rank, world, port, bh, m, n, causal, reduction, out_dir):
     import torch.distributed as dist
 
     from conftest import assert_parity
-    from flash_colreduce_b200.sharding import plan_shards, sharded_colreduce
+    from flash_colreduce_b200.sharding import NativeComm, plan_shards, sharded_colreduce, sharded_colreduce_native
     from oracle import oracle_colreduce
 
     os.environ["MASTER_ADDR"] = "127.0.0.1"
@@ -43,6 +43,20 @@ def _worker(rank, world, port, bh, m, n, causal, reduction, out_dir):
         want = oracle_colreduce(q, k, reduction, causal)[0]
         assert out.shape == want.shape and out.dtype == torch.float16
         assert_parity(out, want, reduction, extra_rtol=2.0 ** -11)
+        # the same through the library's own entry point: shard plan, kernels, ncclAllReduce and the
+        # mean / cast queued by one C call on a communicator the library made
+        comm = NativeComm()
+        try:
+            for _ in range(2):
+                native = sharded_colreduce_native(q[:, spec.head_lo:spec.head_hi].to(dev), k[:, spec.head_lo:spec.head_hi].to(dev),
+                                                  reduction, causal, total_heads=bh, comm=comm, world=world, rank=rank)
+            torch.cuda.synchronize()
+            assert native.shape == want.shape and native.dtype == torch.float16
+            assert_parity(native, want, reduction, extra_rtol=2.0 ** -11)
+            if reduction == "max":
+                assert torch.equal(native, out)  # max does not depend on the order of combination
+        finally:
+            comm.close()
         open(os.path.join(out_dir, f"ok{rank}"), "w").close()
     finally:
         dist.destroy_process_group()
@@ -53,6 +67,7 @@ def _worker(rank, world, port, bh, m, n, causal, reduction, out_dir):
     (1, 3000, 3000, True, "sum"),   # rows of one head split zig-zag over the ranks
     (1, 1500, 520, True, "max"),    # M > N
     (1, 1024, 2048, False, "mean"),
+    (3, 2000, 2000, True, "sum"),   # fewer heads than ranks on four GPUs: idle rank, one rank per head
 ])
 def test_sharded_on_gpus(tmp_path, bh, m, n, causal, reduction):
     import torch.multiprocessing as mp

@@ -45,6 +45,41 @@ def test_row_split_covers_rows_once_and_balances_causal_work():
         assert max(work) <= 1.01 * min(work)
 
 
+def test_c_shard_plan_is_the_same_rule():
+    """fcr_plan_shards (what fcr_colreduce_sharded runs on) against the Python planner."""
+    from flash_colreduce_b200.sharding import native_plan_shards
+
+    for bh in (1, 2, 3, 7, 8, 64):
+        for m in (1, 128, 129, 3000, 131072):
+            for world in (1, 2, 3, 4, 8):
+                for rank in range(world):
+                    a, b = plan_shards(bh, m, world, rank), native_plan_shards(bh, m, world, rank)
+                    assert (a.head_lo, a.head_hi, a.row_ranges, a.needs_reduce) == (b.head_lo, b.head_hi, b.row_ranges, b.needs_reduce)
+    with pytest.raises(ValueError):
+        native_plan_shards(4, 10, 2, 2)
+
+
+def test_sharded_entry_rejects_bad_arguments_before_any_device_work():
+    import ctypes as C
+
+    from flash_colreduce_b200 import _native as nat
+
+    prob = nat.make_problem(1, 2, 256, 256, 64, (2 * 256 * 64, 256 * 64, 64, 1), (2 * 256 * 64, 256 * 64, 64, 1), nat.FCR_F16,
+                            nat.FCR_SUM, True, 0.125)
+    sh = nat.Shard()
+    assert nat.lib.fcr_plan_shards(2, 256, 1, 0, C.byref(sh)) == nat.FCR_OK
+    call = lambda p, s, heads, acc, out: nat.lib.fcr_colreduce_sharded(p, s, heads, None, None, acc, out, nat.FCR_F16, None, 0, None, None)
+    assert call(None, C.byref(sh), 2, None, None) == nat.FCR_ERR_BAD_ARG
+    assert call(C.byref(prob), C.byref(sh), 2, None, None) == nat.FCR_ERR_BAD_ARG and "null acc" in nat.last_error()
+    sh.row_hi[0] = 300  # beyond M
+    assert call(C.byref(prob), C.byref(sh), 2, None, None) == nat.FCR_ERR_BAD_ARG and "row range" in nat.last_error()
+    sh.row_hi[0] = 256
+    sh.head_hi = 3      # three heads against a two-head local problem
+    assert call(C.byref(prob), C.byref(sh), 3, None, None) == nat.FCR_ERR_BAD_ARG and "exactly the shard's heads" in nat.last_error()
+    assert nat.lib.fcr_comm_init(None, 2, 0, None) == nat.FCR_ERR_BAD_ARG
+    assert nat.lib.fcr_comm_destroy(None) == nat.FCR_OK
+
+
 def test_bad_arguments():
     with pytest.raises(ValueError):
         plan_shards(4, 10, 2, 2)
