@@ -52,13 +52,21 @@ def flash_colreduce_host(
         out = torch.empty((b, h, n), dtype=query.dtype, pin_memory=True)
     if out.numel() == 0:
         return out
-    if group_heads is None:
-        # About eight groups per batch entry: the first group's copy is the only one that is not
-        # hidden behind kernels, so it should be a small share, yet every launch should still
-        # carry many heads.  Groups are capped at 512 MiB of input.
+    ramp = group_heads is None
+    if ramp:
+        # About eight groups per batch entry, capped at 512 MiB of input, so that every launch
+        # carries many heads.  The first group's copy is the only one that is not hidden behind
+        # kernels: the very first groups are small (1, 1, 2, 4, ... heads) and grow to that size.
         per_head = (m + n) * d * query.element_size()
         group_heads = max(1, min(-(-h // 8), (512 << 20) // max(per_head, 1)))
-    groups = [(bi, h0, min(h0 + group_heads, h)) for bi in range(b) for h0 in range(0, h, group_heads)]
+    groups = []
+    for bi in range(b):
+        h0, size = 0, (1 if ramp and bi == 0 else group_heads)
+        while h0 < h:
+            groups.append((bi, h0, min(h0 + size, h)))
+            h0 += size
+            if len(groups) >= 2:
+                size = min(2 * size, group_heads)
     with torch.cuda.device(device):
         compute = torch.cuda.current_stream(device)
         ctx = _context(device, min(group_heads, h), m, n, d, query.dtype)
