@@ -17,7 +17,7 @@ lines up with ``benchmarks/results/*.log``.  Every row times
   and query rows when its (B,H,M,N) matrix does not fit, like ``chunked_run``.
 
 ``--configs`` appends the configurations the throughput metric is quoted on
-(square 512 x 3 reductions, causal decode 128 x 4096 x 3 reductions, the
+(the 256-square CPU-sized case, square 512 x 3 reductions, causal decode 128 x 4096 x 3 reductions, the
 8192-square VLM pruning shape, an 8-head shard of the 131072-square long
 context).  ``--slice-m`` also times this library on query-row slices of one
 larger tensor (non-contiguous views, the call pattern ``chunked_run`` produces).
@@ -42,7 +42,8 @@ SHAPES = (
 )
 
 METRIC_CONFIGS = (
-    [dict(b=8, h=16, m=512, n=512, d=64, is_causal=False, reduction=r, tag="c2") for r in ("sum", "mean", "max")]
+    [dict(b=2, h=4, m=256, n=256, d=64, is_causal=False, reduction="sum", tag="c1")]
+    + [dict(b=8, h=16, m=512, n=512, d=64, is_causal=False, reduction=r, tag="c2") for r in ("sum", "mean", "max")]
     + [dict(b=1, h=32, m=128, n=4096, d=128, is_causal=True, reduction=r, tag="c3") for r in ("sum", "mean", "max")]
     + [dict(b=4, h=32, m=8192, n=8192, d=128, is_causal=True, reduction="mean", tag="c4")]
     + [dict(b=1, h=8, m=131072, n=131072, d=128, is_causal=True, reduction="sum", tag="c5 shard (8 of 64 heads)")]
