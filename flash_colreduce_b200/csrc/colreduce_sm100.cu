@@ -182,27 +182,16 @@ struct SmemLayout {
 
 // Bounded mbarrier wait.  Returns false when the wait limit expired here or in
 // another thread of the CTA (the abort flag); the caller then leaves its loop.
-#ifndef FCR_BACKOFF_SERVICE_NS
-#define FCR_BACKOFF_SERVICE_NS 0
-#endif
-#ifndef FCR_BACKOFF_FOLD_NS
-#define FCR_BACKOFF_FOLD_NS 0
-#endif
-// A failed mbarrier try_wait returns after some tens of nanoseconds, so a waiting warp polls; between
-// polls it may sleep (BACKOFF_NS > 0), which takes its polling instructions out of the issue ports
-// at the price of waking up late.  The TMA and MMA warps wait most of the time and have slack (ring
-// depth, two accumulator buffers per sub-tile); the fold warps' wake-up delay is on the critical path.
-constexpr int kServiceBackoffNs = FCR_BACKOFF_SERVICE_NS;
-constexpr int kFoldBackoffNs = FCR_BACKOFF_FOLD_NS;
-
-template <int BACKOFF_NS>
+// A failed mbarrier try_wait comes back after some tens of nanoseconds (whatever the suspend-time
+// hint), so a waiting warp polls.  Letting the waiting warps sleep between polls was measured
+// (100 ns to 1 us for the TMA and MMA warps, 50 and 200 ns for the fold warps): no timing changed by
+// more than the run-to-run noise, so they simply poll.
 __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                          const PassParams& p, int code) {
   if (ptx::mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   uint32_t spins = 0;
   while (true) {
-    if (BACKOFF_NS > 0) __nanosleep(BACKOFF_NS);
     if (ptx::mbar_try_wait(bar, parity)) return true;
     if ((++spins & 7u) == 0) {
       if (*abort_flag) return false;
@@ -216,12 +205,10 @@ __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile
 }
 // Same, with a warp-uniform result so that .sync.aligned instructions that
 // follow are executed by all 32 lanes or by none.
-// (`kBackoff` is a constant each warp role defines for itself.)
-#define WAIT(bar, par, code) wait_bar_warp<kBackoff>(bar, par, abort_flag, p, code)
-template <int BACKOFF_NS>
+#define WAIT(bar, par, code) wait_bar_warp(bar, par, abort_flag, p, code)
 __device__ __forceinline__ bool wait_bar_warp(uint32_t bar, uint32_t parity,
                                               volatile int* abort_flag, const PassParams& p, int code) {
-  const bool ok = wait_bar<BACKOFF_NS>(bar, parity, abort_flag, p, code);
+  const bool ok = wait_bar(bar, parity, abort_flag, p, code);
   return __all_sync(0xffffffffu, ok);
 }
 
@@ -350,7 +337,6 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
 
   if (warp == kProducerWarp) {
     // ------------------------------------------------------------ TMA warp
-    constexpr int kBackoff = kServiceBackoffNs;
     // Work items are handed out dynamically: the first is the CTA's own index,
     // later ones come from a global counter (fetched one item early, so that the
     // atomic's latency is hidden).  Each item is decoded here once and announced
@@ -472,7 +458,6 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
     }
   } else if (warp >= kMmaWarp) {
     // ----------------------------------------------------------- MMA warps
-    constexpr int kBackoff = kServiceBackoffNs;
     // One issuing warp per stationary sub-tile: tcgen05.mma issue blocks while
     // the tensor pipe's short queue is full, so with a single issuer the pipe
     // drains during that warp's barrier handshakes; with two, one warp's
@@ -581,7 +566,6 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
     }
   } else {
     // -------------------------------------------------------- softmax warps
-    constexpr int kBackoff = kFoldBackoffNs;
     // Warp w reads tensor-memory lanes 32*(w%4).. (a hardware rule), belongs to
     // stationary sub-tile a and to fold group `part` of it: it folds the accumulator
     // tiles of sub-tile a that land in buffer `part`, all 128 columns of each.

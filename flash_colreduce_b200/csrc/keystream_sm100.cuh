@@ -60,7 +60,6 @@ template <int PHASE, int DPAD, int RED>
 __global__ void __launch_bounds__(kKsThreads, 1)
 keystream_kernel(const __grid_constant__ CUtensorMap tmap_q,
                  const __grid_constant__ CUtensorMap tmap_k, const PassParams p) {
-  constexpr int kBackoff = 0;  // these kernels are bound by the key stream from HBM: the waiting warps just poll
   static_assert(PHASE == PH_ROWS || PHASE == PH_COLS, "rows or columns pass");
   using L = KeyStreamSmem<DPAD>;
   constexpr int KR = L::KR;
