@@ -19,7 +19,8 @@
 // softmax warps (two warpgroups of four warps per stationary tile, each folding
 // every other accumulator tile of it), warp 16 issues the TMA loads and hands
 // out work items, warps 17 and 18 issue tcgen05.mma (one per stationary tile;
-// warp 17 also owns the tensor-memory allocation).
+// warp 17 also owns the tensor-memory allocation).  The columns pass of the max
+// reduction has two more MMA warps (672 threads): one issuer per accumulator buffer.
 //
 // The arithmetic follows the reference kernel: scores are scaled by
 // scale/ln(2) and exponentials are base 2 (flash_colreduce/flash.py:59-78,
@@ -56,13 +57,11 @@ constexpr int kFoldGroups = 2;
 constexpr int kSoftmaxWarps = 4 * kSubTiles * kFoldGroups;
 constexpr int kProducerWarp = kSoftmaxWarps;
 constexpr int kMmaWarp = kSoftmaxWarps + 1;   // issues the MMAs of sub-tile 0, owns the TMEM allocation
-#ifndef FCR_MMA_PER_BUFFER
-#define FCR_MMA_PER_BUFFER 0
-#endif
-// MMA-issuing warps: one per stationary sub-tile, or one per accumulator buffer (two per sub-tile)
-constexpr bool kMmaPerBuffer = FCR_MMA_PER_BUFFER != 0;
-constexpr int kMmaWarps = kMmaPerBuffer ? 2 * kSubTiles : kSubTiles;
-constexpr int kThreads = (kSoftmaxWarps + 1 + kMmaWarps) * 32;
+// MMA-issuing warps: one per stationary sub-tile, except in the columns pass of the max reduction,
+// which has one per accumulator buffer (two per sub-tile).  That pass takes no exponentials, its
+// folds are short, and with one issuer per sub-tile the tensor pipe waited for the issuer's barrier
+// handshakes (8192-square, 128 heads: 1.17 -> 0.94 ms); the other passes are bound by the folds and
+// lose to the extra warps' registers (measured 3-6 % slower), so they keep one issuer per sub-tile.
 constexpr int kTmemCols = 512;
 constexpr int kSpan = kTile;  // columns of an accumulator tile one thread folds: all of them
 #ifndef FCR_CHUNK_ROWS
@@ -227,12 +226,21 @@ __device__ __forceinline__ void store_out(void* out, int out_dtype, size_t idx, 
   }
 }
 
+template <int PHASE, int RED>
+__host__ __device__ constexpr bool mma_per_buffer() { return PHASE == PH_COLS && RED == RED_MAX; }
+template <int PHASE, int RED>
+__host__ __device__ constexpr int pass_threads() {
+  return (kSoftmaxWarps + 1 + (mma_per_buffer<PHASE, RED>() ? 2 * kSubTiles : kSubTiles)) * 32;
+}
+
 template <int PHASE, int DPAD, int RED, bool SHORT>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__((pass_threads<PHASE, RED>()), 1)
 pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
             const __grid_constant__ CUtensorMap tmap_strm, const PassParams p) {
   using L = SmemLayout<DPAD, SHORT>;
   constexpr int KS = L::KS, KR = L::KR;
+  constexpr bool kMmaPerBuffer = mma_per_buffer<PHASE, RED>();
+  constexpr int kMmaWarps = kMmaPerBuffer ? 2 * kSubTiles : kSubTiles;
   // The 128-byte swizzle of the operand tiles needs a 1024-byte aligned base;
   // the kernel uses no static shared memory, so the dynamic window starts there.
   extern __shared__ __align__(1024) uint8_t smem[];
@@ -458,12 +466,12 @@ pass_kernel(const __grid_constant__ CUtensorMap tmap_stat,
     }
   } else if (warp >= kMmaWarp) {
     // ----------------------------------------------------------- MMA warps
-    // One issuing warp per stationary sub-tile: tcgen05.mma issue blocks while
-    // the tensor pipe's short queue is full, so with a single issuer the pipe
-    // drains during that warp's barrier handshakes; with two, one warp's
-    // handshakes overlap the other's MMAs.
+    // One issuing warp per stationary sub-tile (per accumulator buffer in the max columns pass):
+    // tcgen05.mma issue blocks while the tensor pipe's short queue is full, so with a single
+    // issuer the pipe drains during that warp's barrier handshakes; with several, one warp's
+    // handshakes overlap another's MMAs.
     const int a = (warp - kMmaWarp) % kSubTiles;
-    const int my_buf = (warp - kMmaWarp) / kSubTiles;  // only with one issuer per accumulator buffer
+    const int my_buf = (warp - kMmaWarp) / kSubTiles;  // non-zero only with one issuer per accumulator buffer
     // Accumulator buffer of a tile = (its index within the work item + the item's parity) mod 2,
     // so that the warpgroup that folds it does not depend on which items this CTA happened to get;
     // tm_use[b] counts the uses of buffer b and gives its barrier phase.
@@ -1063,7 +1071,7 @@ static int launch_pass(const CUtensorMap& stat, const CUtensorMap& strm, const P
   // Every pass kernel may begin its set-up while the kernel before it in the stream drains (they all
   // wait for that kernel's completion before touching global memory): the columns pass follows the rows
   // pass or its combine kernel, the rows pass the previous call's last kernel.
-  e = launch_kernel(kern, dim3(ctas), dim3(kThreads), smem, stream, true, stat, strm, pp);
+  e = launch_kernel(kern, dim3(ctas), dim3(pass_threads<PHASE, RED>()), smem, stream, true, stat, strm, pp);
   if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "pass kernel launch");
   return FCR_OK;
