@@ -51,7 +51,7 @@ class ClockSampler:
     """Samples SM clock and throttle reasons through NVML while the timed region runs (read-only)."""
 
     def __init__(self, index: int):
-        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self.samples, self.reasons, self.max_mhz, self.power = [], set(), None, []
         self._stop = threading.Event()
         self._thread = None
         try:
@@ -75,6 +75,10 @@ class ClockSampler:
         while not self._stop.is_set():
             try:
                 self.samples.append(nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM))
+                try:
+                    self.power.append(nv.nvmlDeviceGetPowerUsage(self.handle) / 1000.0)
+                except Exception:
+                    pass
                 try:
                     mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self.handle)
                 except Exception:
@@ -101,7 +105,9 @@ class ClockSampler:
         if not self.samples:
             return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons)}
         s = sorted(self.samples)
-        return {"sm_mhz": s[len(s) // 2], "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons)}
+        w = sorted(self.power)
+        return {"sm_mhz": s[len(s) // 2], "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "power_w": w[len(w) // 2] if w else None}
 
 
 def _use_all_host_threads() -> int:
