@@ -42,3 +42,15 @@ def test_dense_definition_matches_oracle(red, causal):
     torch.testing.assert_close(got, oracle_colreduce(q, k, red, causal), rtol=1e-5, atol=1e-7)
     with pytest.raises(ValueError, match="Invalid reduction"):
         fc.naive_colreduce(q, k, "prod")
+
+
+def test_signature_is_the_reference_operator_signature():
+    """flash_colreduce(query, key, reduction, is_causal=False, scale=None), flash_colreduce/flash.py:311-317."""
+    import inspect
+
+    params = inspect.signature(fc.flash_colreduce).parameters
+    assert list(params) == ["query", "key", "reduction", "is_causal", "scale"]
+    assert params["is_causal"].default is False and params["scale"].default is None
+    assert all(p.kind is inspect.Parameter.POSITIONAL_OR_KEYWORD for p in params.values())
+    naive = inspect.signature(fc.naive_colreduce).parameters
+    assert list(naive)[:5] == ["query", "key", "reduction", "is_causal", "scale"]  # naive.py:8-14
