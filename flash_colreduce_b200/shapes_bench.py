@@ -1,6 +1,6 @@
 """Latency / peak-memory table over the reference's 20 benchmark shapes, side by side.
 
-    python -m flash_colreduce_b200.shapes_bench [--reference-path DIR] [--naive] [--configs]
+    python -m flash_colreduce_b200.shapes_bench [--reference-path DIR] [--naive] [--configs] [--cpu]
                                                 [--slice-m] [--seconds S] [--json F] [--md F]
 
 Counterpart of the reference's ``benchmarks/run.py`` (shape list :11-56,
@@ -19,7 +19,7 @@ lines up with ``benchmarks/results/*.log``.  Every row times
 ``--configs`` appends the configurations the throughput metric is quoted on
 (the 256-square CPU-sized case, square 512 x 3 reductions, causal decode 128 x 4096 x 3 reductions, the
 8192-square VLM pruning shape, an 8-head shard of the 131072-square long
-context).  ``--slice-m`` also times this library on query-row slices of one
+context); ``--cpu`` adds the definition on the host cores (fp32, all threads) for them.  ``--slice-m`` also times this library on query-row slices of one
 larger tensor (non-contiguous views, the call pattern ``chunked_run`` produces).
 """
 from __future__ import annotations
@@ -128,7 +128,7 @@ def _label(cfg) -> str:
     return s
 
 
-def run_row(cfg, ref, want_naive: bool, slice_m: bool, seconds: float, dev) -> dict:
+def run_row(cfg, ref, want_naive: bool, slice_m: bool, seconds: float, dev, want_cpu: bool = False) -> dict:
     b, h, m, n, d, causal = cfg["b"], cfg["h"], cfg["m"], cfg["n"], cfg["d"], cfg["is_causal"]
     red = cfg.get("reduction", "sum")
     q = torch.randn(b, h, m, d, device=dev, dtype=torch.float16)
@@ -153,6 +153,9 @@ def run_row(cfg, ref, want_naive: bool, slice_m: bool, seconds: float, dev) -> d
         naive = lambda: chunked_call(naive_op, q, k, red, causal)
         nlat = measure_latency(naive, min_iters=3, seconds=min(seconds, 0.5))
         row.update(naive_ms=nlat * 1e3, naive_mb=measure_memory(naive) / 2**20, speedup_vs_naive=nlat / lat)
+    if want_cpu and "tag" in cfg and b * h * m * n <= 2**35:
+        ms, threads, how = cpu_definition_ms(cfg, ref, q, k, red)
+        row.update(cpu_ms=ms, cpu_threads=threads, cpu_how=how, speedup_vs_cpu=ms / (lat * 1e3))
     if slice_m and m >= 512:
         # the same rows as two query-row slices of a tensor twice as long: non-contiguous views
         big = torch.randn(b, h, 2 * m, d, device=dev, dtype=torch.float16)
@@ -163,21 +166,49 @@ def run_row(cfg, ref, want_naive: bool, slice_m: bool, seconds: float, dev) -> d
     return row
 
 
+def cpu_definition_ms(cfg, ref, q, k, red):
+    """The materialising definition on the host cores in fp32 (all threads), as a reported baseline:
+    median of five calls after a warm-up for problems of up to 2^28 scores, else eight (batch, head)
+    pairs spread over the problem, one at a time, scaled to all of them (labelled as extrapolated)."""
+    import os
+
+    torch.set_num_threads(os.cpu_count() or 1)
+    op = ref.naive_colreduce if ref is not None else naive_colreduce
+    b, h, m, n = cfg["b"], cfg["h"], cfg["m"], cfg["n"]
+    qc, kc = q.float().cpu(), k.float().cpu()
+    if b * h * m * n <= 2**28:
+        op(qc, kc, reduction=red, is_causal=cfg["is_causal"])
+        times = []
+        for _ in range(5):
+            t0 = time.perf_counter()
+            op(qc, kc, reduction=red, is_causal=cfg["is_causal"])
+            times.append(time.perf_counter() - t0)
+        return sorted(times)[2] * 1e3, torch.get_num_threads(), "whole problem, median of 5"
+    pairs = [(i * b * h) // 8 for i in range(8)]
+    t0 = time.perf_counter()
+    for bh in pairs:
+        bi, hi = divmod(bh, h)
+        op(qc[bi:bi + 1, hi:hi + 1], kc[bi:bi + 1, hi:hi + 1], reduction=red, is_causal=cfg["is_causal"])
+    per_head = (time.perf_counter() - t0) / len(pairs)
+    return per_head * b * h * 1e3, torch.get_num_threads(), f"extrapolated from {len(pairs)} of {b * h} heads"
+
+
 def _fmt(row, key, spec="{:.3f}"):
     return spec.format(row[key]) if key in row else "-"
 
 
 def to_markdown(rows, gpu: str) -> str:
     head = ("| configuration | this library ms | reference (Triton) ms | speed-up vs reference | naive ms | speed-up vs naive | "
-            "this MB | reference MB | naive MB | Gscores/s | TFLOP/s | max abs diff vs reference |")
-    lines = [f"GPU: {gpu}", "", head, "|" + "---|" * 12]
+            "this MB | reference MB | naive MB | Gscores/s | TFLOP/s | max abs diff vs reference | definition on host cores ms |")
+    lines = [f"GPU: {gpu}", "", head, "|" + "---|" * 13]
     for r in rows:
         ref_ms = _fmt(r, "reference_ms") if "reference_error" not in r else r["reference_error"]
         lines.append(
             f"| {r['config']} | {r['ours_ms']:.3f} | {ref_ms} | {_fmt(r, 'speedup_vs_reference', '{:.2f}')} | "
             f"{_fmt(r, 'naive_ms')} | {_fmt(r, 'speedup_vs_naive', '{:.2f}')} | {r['ours_mb']:.1f} | "
             f"{_fmt(r, 'reference_mb', '{:.1f}')} | {_fmt(r, 'naive_mb', '{:.1f}')} | {r['gscores_per_s']:.1f} | "
-            f"{r['tflops']:.1f} | {_fmt(r, 'max_abs_diff_vs_reference', '{:.2e}')} |")
+            f"{r['tflops']:.1f} | {_fmt(r, 'max_abs_diff_vs_reference', '{:.2e}')} | "
+            + (f"{r['cpu_ms']:.1f} ({r['cpu_threads']} threads, {r['cpu_how']})" if "cpu_ms" in r else "-") + " |")
     return "\n".join(lines) + "\n"
 
 
@@ -189,6 +220,8 @@ def main() -> None:
     ap.add_argument("--configs", action="store_true", help="append the metric's own configurations")
     ap.add_argument("--only-configs", action="store_true", help="skip the 20 shapes")
     ap.add_argument("--slice-m", action="store_true", help="also time this library on query-row slices (strided views)")
+    ap.add_argument("--cpu", action="store_true",
+                    help="also time the materialising definition on the host cores for the metric's configurations")
     ap.add_argument("--seconds", type=float, default=1.0, help="length of each warm-up and each timed run")
     ap.add_argument("--json", default=None)
     ap.add_argument("--md", default=None)
@@ -200,7 +233,7 @@ def main() -> None:
     shapes = ([] if args.only_configs else list(SHAPES)) + (list(METRIC_CONFIGS) if args.configs or args.only_configs else [])
     rows = []
     for cfg in shapes:
-        row = run_row(cfg, ref, args.naive, args.slice_m, args.seconds, dev)
+        row = run_row(cfg, ref, args.naive, args.slice_m, args.seconds, dev, args.cpu)
         print(json.dumps(row), flush=True)
         rows.append(row)
     if args.json:
