@@ -64,6 +64,14 @@ def _problem_and_workspace_bytes(key_tuple, device):
 
 
 def _launch(query, key, out, out_code, reduction_code, is_causal, scale, causal_offset, mean_M, mean_N):
+    """Plans (cached), allocates the workspace and queues the kernels on the current stream.
+
+    No synchronisation.  A bounded wait that expired inside a kernel of an EARLIER call on this
+    device is reported here: the library finds the status in its mailbox in mapped host memory
+    and returns FCR_ERR_DEVICE_TIMEOUT instead of launching, which ``nat.check`` turns into a
+    ``RuntimeError``.  ``FCR_DEBUG_SYNC=1`` additionally synchronises after every call and reads
+    the status words of the call's own workspace.
+    """
     b, h, m, _ = query.shape
     n = key.shape[2]
     q = _tma_ready(query)
